@@ -6,7 +6,8 @@ starts takes it again.
 
 What is kept per slot is declared by the model's mixers, one *need* per schedule entry:
 
-  KvNeed     keys and values of every position (window 0) or of the last `window` positions.
+  KvNeed     keys and values of every position (window 0) or of the last `window` positions (or one row per
+             position that serves as both, `planes=1`).
              Storage is handed out in pages of PAGE_TOKENS positions, so a sequence holds
              ceil(length / PAGE_TOKENS) pages and nothing more: the cache is sized by the
              number of live tokens, not by slots x longest sequence.
@@ -42,6 +43,8 @@ class KvNeed:
     kv_heads: int
     head_dim: int
     window: int = 0  # 0: every earlier position
+    planes: int = 2  # rows kept per position and head: keys and values, or 1 for a mixer whose keys are its values
+                     # (the shared latent of a latent attention)
 
 
 @dataclass(frozen=True)
@@ -55,7 +58,7 @@ class KvSite:
 
     def __init__(self, group: "KvGroup", index: int):
         self.group = group
-        self.storage = group.storage[index]  # [pages, 2, kv_heads, PAGE_TOKENS, head_dim]
+        self.storage = group.storage[index]  # [pages, planes, kv_heads, PAGE_TOKENS, head_dim]
         self.table = group.table
         self.kv_heads = group.need.kv_heads
         self.head_dim = group.need.head_dim
@@ -70,7 +73,7 @@ class KvGroup:
         self.pages = PageAllocator(n_pages)
         self.pages_per_seq = pages_per_seq
         # zeroed once: no kernel reads beyond a sequence's length, stale data is finite anyway
-        self.storage = torch.zeros((len(self.entries), n_pages, 2, need.kv_heads, PAGE_TOKENS, need.head_dim),
+        self.storage = torch.zeros((len(self.entries), n_pages, need.planes, need.kv_heads, PAGE_TOKENS, need.head_dim),
                                    dtype=dtype, device=device)
         self.table = torch.full((n_slots, pages_per_seq), -1, dtype=torch.int32, device=device)
         self._host_table = torch.full((n_slots, pages_per_seq), -1, dtype=torch.int32)
@@ -281,7 +284,7 @@ class SequenceCache:
         """Bytes of keys and values that one single-token step reads for sequences of these lengths."""
         total = 0
         for g in self.kv_groups:
-            per_token = len(g.entries) * 2 * g.need.kv_heads * g.need.head_dim * g.storage.element_size()
+            per_token = len(g.entries) * g.need.planes * g.need.kv_heads * g.need.head_dim * g.storage.element_size()
             total += per_token * sum(min(n, g.need.window) if g.need.window > 0 else n for n in lengths)
         return total
 

@@ -3,10 +3,11 @@ from .registry import (ModelConfig, config_class_for, config_from_dict, load_con
                        registered_architectures)
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
+from .mefepel import MefepelConfig
 from .presets import preset_config, preset_dict, preset_names
 
 __all__ = [
     "resolve_dtype", "ModelConfig", "config_class_for", "config_from_dict", "load_config", "register_architecture",
-    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config",
+    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config", "MefepelConfig",
     "preset_config", "preset_dict", "preset_names",
 ]

@@ -51,7 +51,7 @@ def registered_architectures() -> list[str]:
 
 
 def config_class_for(data: Mapping[str, Any]) -> type:
-    names = data.get("architectures") or []
+    names = data.get("architectures") or data.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     name = names[0] if names else _MODEL_TYPES.get(str(data.get("model_type", "")))

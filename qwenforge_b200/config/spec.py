@@ -73,6 +73,9 @@ class ModelSpec:
     # tensor names that files may hold although no part asks for them, each with the wanted tensor it must
     # equal (a stored copy of a shared table); a copy that differs is an error
     redundant_tensors: Mapping[str, str] = field(default_factory=dict)
+    # tensor names that files may hold and that the model does not read (say, the norms of a feed-forward that a layer
+    # of this model does not have)
+    ignored_tensors: tuple = ()
 
     def validate(self) -> None:
         if not self.schedule:

@@ -50,3 +50,27 @@ QF_EXPORT int qf_swiglu(int is_bf16, const void* gu, void* out, int rows, int in
         code = (int)launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total);
     return code;
 }
+
+// The gate of a feed-forward with clamped halves, on the fused [gate | up] projection, in float32:
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, float limit, float alpha) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter, c = i % inter;
+        const float g = fminf(Num<T>::to_f(gu[t * 2 * inter + c]), limit);
+        const float u = fminf(fmaxf(Num<T>::to_f(gu[t * 2 * inter + inter + c]), -limit), limit);
+        out[i] = Num<T>::from_f(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+QF_EXPORT int qf_clamped_glu(int is_bf16, const void* gu, void* out, int rows, int inter, float limit, float alpha,
+                             cudaStream_t stream) {
+    const size_t total = (size_t)rows * inter;
+    if (total == 0) return 0;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    if (is_bf16)
+        return (int)launch_pdl(clamped_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, inter, total, limit, alpha);
+    return (int)launch_pdl(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total, limit, alpha);
+}

@@ -18,6 +18,10 @@
 // No block waits for another. (Merging the splits of a thread-block cluster through distributed shared memory
 // instead was measured slower, and so was a variant of sixteen warps with half a page each.)
 // The kernel is launched as a programmatic dependent of the kernel before it.
+// `sinks` (float32 per query head, or null): a logit that joins the softmax's denominator once, unscaled, with no key and
+// no value; it is added where a row's runs come together (not with fold_later: the caller's fold knows no sinks).
+// `shared_values`: the values are the keys themselves (pages of one plane, as a latent attention keeps them): half a
+// page is fetched once and read as both.
 #include <algorithm>
 
 #include "tma.cuh"
@@ -102,7 +106,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                     const int* __restrict__ cu_q, const int4* __restrict__ plan, KvSite<bf16> site, int n_heads, int chunks, float scale_log2,
                     int window, int max_splits, int n_seqs, int fold_later, float* __restrict__ part_o,
-                    float* __restrict__ part_ml, int* __restrict__ counters, int* err, unsigned long long* stamps) {
+                    float* __restrict__ part_ml, int* __restrict__ counters, int* err, unsigned long long* stamps,
+                    const float* __restrict__ sinks, int shared_values) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
     // measuring aid: if `stamps` is given, thread 0 leaves nanosecond time stamps of the block's phases in stamps[block][8]
     auto stamp = [&](int phase) {
@@ -200,15 +205,15 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             bf16* vb = kb + HALF * LD;
             if (TMA) {
                 if (lane == 0) {
-                    // row of the cache seen as one matrix [pages * 2 * kv_heads * 64][D]
-                    const long long k_row = ((long long)page * 2 * site.kv_heads + kvh) * QF_PAGE + (i & 1) * HALF;
+                    // row of the cache seen as one matrix [pages * planes * kv_heads * 64][D]
+                    const long long k_row = (long long)page * (site.page_elems / D) + (long long)kvh * QF_PAGE + (i & 1) * HALF;
                     const long long v_row = k_row + (long long)site.kv_heads * QF_PAGE;
                     uint64_t* bar = &bars[warp][i & 1];
-                    mbar_expect_tx(bar, 2 * HALF * D * 2);
+                    mbar_expect_tx(bar, (shared_values ? 1 : 2) * HALF * D * 2);
 #pragma unroll
                     for (int cb = 0; cb < D / 64; ++cb) {
                         tma_load_2d(kb + (size_t)cb * HALF * 64, &kv_map, cb * 64, (int)k_row, bar);
-                        tma_load_2d(vb + (size_t)cb * HALF * 64, &kv_map, cb * 64, (int)v_row, bar);
+                        if (!shared_values) tma_load_2d(vb + (size_t)cb * HALF * 64, &kv_map, cb * 64, (int)v_row, bar);
                     }
                 }
             } else {
@@ -219,7 +224,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                 for (int j = lane; j < HALF * CH; j += 32) {
                     const int r = j / CH, c = (j % CH) * 8;
                     cp_async_16(kb + (size_t)r * LD + c, kp + (size_t)r * D + c, true);
-                    cp_async_16(vb + (size_t)r * LD + c, vp + (size_t)r * D + c, true);
+                    if (!shared_values) cp_async_16(vb + (size_t)r * LD + c, vp + (size_t)r * D + c, true);
                 }
             }
         }
@@ -276,7 +281,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         }
         if (live) {
             const bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
-            const bf16* vb = kb + HALF * LD;
+            const bf16* vb = shared_values ? kb : kb + HALF * LD;
             float s[4][4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
@@ -409,6 +414,15 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             float l = 0.f;
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
+            if (sinks) {  // the sink's term, in base-2 units like the scores, on a common maximum
+                float m_all = m_s[0][r];
+#pragma unroll
+                for (int w = 1; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, m_s[w][r]);
+                const float s2 = sinks[head0 + r] * 1.4426950408889634f, m_new = fmaxf(m_all, s2);
+                const float keep = exp2f(m_all - m_new);
+                l = l * keep + exp2f(s2 - m_new);
+                num *= keep;
+            }
             out_row[i] = __float2bfloat16_rn(l > 0.f ? num / l : 0.f);
         } else {
             part_o[(part_row0 + (size_t)r * max_splits + split) * D + d] = num;
@@ -501,7 +515,13 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
 #pragma unroll
         for (int x = 0; x < 2; ++x)
             if (live[x]) {
-                const float inv = den[x] > 0.f ? 1.f / den[x] : 0.f;
+                float keep = 1.f;
+                if (sinks) {
+                    const float s2 = sinks[head0 + (i0 + x * DEC_THREADS) / D4] * 1.4426950408889634f, m_new = fmaxf(big[x], s2);
+                    keep = exp2f(big[x] - m_new);
+                    den[x] = den[x] * keep + exp2f(s2 - m_new);
+                }
+                const float inv = den[x] > 0.f ? keep / den[x] : 0.f;
                 uint2 packed;
                 packed.x = pack_bf16(num[x].x * inv, num[x].y * inv);
                 packed.y = pack_bf16(num[x].z * inv, num[x].w * inv);
@@ -565,7 +585,7 @@ template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int4* plan, void* base, const int* table,
                   long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
                   int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err,
-                  unsigned long long* stamps, cudaStream_t stream) {
+                  unsigned long long* stamps, const float* sinks, int shared_values, cudaStream_t stream) {
     constexpr int WARPS = decode_warps(D);
     constexpr bool TMA = decode_tma(D);
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
@@ -582,7 +602,7 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
     dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, D, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
                            (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
-                           n_seqs, fold_later, part_o, part_ml, counters, err, stamps);
+                           n_seqs, fold_later, part_o, part_ml, counters, err, stamps, sinks, shared_values);
 }
 
 // How many 16-byte units a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode
@@ -613,14 +633,14 @@ QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, cons
 static int decode_run(const void* q, void* out, const int* cu_q, const void* plan, void* base, const int* table,
                       long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                       float scale, int window, int n_splits, int fold_later, float* part_o, float* part_ml, int* counters,
-                      int* err, unsigned long long* stamps, cudaStream_t stream) {
+                      int* err, unsigned long long* stamps, const float* sinks, int shared_values, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan) return (int)cudaErrorInvalidValue;
+    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan || (fold_later && sinks)) return (int)cudaErrorInvalidValue;
     if (fold_later ? (!part_o || !part_ml) : !out) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                   \
     case DIM:                                                                                                          \
         return launch<DIM>(q, out, cu_q, (const int4*)plan, base, table, page_elems, table_stride, kv_heads, n_heads, \
-                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, stream);
+                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, sinks, shared_values, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -637,7 +657,17 @@ QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, con
                                   int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
                                   float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
     return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
-                      window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, stream);
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, nullptr, 0, stream);
+}
+
+// The same with the two options at the top of the file: `sinks` float32 [n_heads] or null, `shared_values` 0 or 1.
+QF_EXPORT int qf_attention_decode_ex(const void* q, void* out, const int* cu_q, const void* plan, void* base,
+                                     const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
+                                     int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
+                                     float* part_o, float* part_ml, int* counters, int* err, const float* sinks,
+                                     int shared_values, cudaStream_t stream) {
+    return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, sinks, shared_values, stream);
 }
 
 // A measuring aid: the same launch, with every block's thread 0 writing nanosecond time stamps to stamps[block][8]:
@@ -650,7 +680,7 @@ QF_EXPORT int qf_attention_decode_stamped(const void* q, void* out, const int* c
                                           int fold_later, float* part_o, float* part_ml, int* counters, int* err,
                                           unsigned long long* stamps, cudaStream_t stream) {
     return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
-                      window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, stream);
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, nullptr, 0, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

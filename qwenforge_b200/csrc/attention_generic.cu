@@ -12,6 +12,11 @@
 //
 // Query i at position p sees keys j with max(0, p - window + 1) <= j <= p (window 0: all j <= p).
 //
+// Two options that other kinds of attention need. `sinks` (float32, one per query head, or null): a learned logit that
+// joins the softmax's denominator once, unscaled, with no key and no value. `shared_values`: the values are the keys
+// themselves (a cache of one plane per page, as a latent attention keeps it: every query head reads the one latent
+// "head" as key and as value).
+//
 // Steps of one token per sequence (decoding) give only sequences x kv heads blocks, each walking a whole sequence. For
 // them the keys are cut into chunks of GEN_CHUNK positions at absolute multiples of GEN_CHUNK: a block per (sequence,
 // kv head, chunk) leaves its rows' maximum, sum and unnormalised output in scratch, and a second kernel folds a row's
@@ -25,15 +30,16 @@
 #define WARPS 8
 #define ROWS_PER_WARP 4
 #define MAX_ROWS (WARPS * ROWS_PER_WARP)
-#define MAX_DPL 8           // head_dim <= 32 * MAX_DPL
+#define MAX_DPL_SMALL 8     // head_dim <= 32 * MAX_DPL: 256 for the common case, 512 for wide (latent) heads
+#define MAX_DPL_WIDE 16
 #define GEN_CHUNK 256       // keys per block of the split form; a multiple of KT
 
-template <typename T, bool SPLIT>
+template <typename T, bool SPLIT, int MAX_DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int* __restrict__ cu_q,
                          const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<T> site, int n_heads,
                          int group_chunk, int tokens_per_tile, float scale, int window, float* __restrict__ part_o,
-                         float* __restrict__ part_ml, int* err) {
+                         float* __restrict__ part_ml, int* err, const float* __restrict__ sinks, int shared_values) {
     extern __shared__ float smem[];
     const int D = site.head_dim, G = n_heads / site.kv_heads;
     const int chunks = (G + group_chunk - 1) / group_chunk;
@@ -106,7 +112,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
                 const T* kp = kv_row(site, slot, kj, kvh, 0);
                 if (kp) {
                     kval = Num<T>::to_f(kp[d]);
-                    vval = Num<T>::to_f(kp[(size_t)site.kv_heads * QF_PAGE * D + d]);
+                    vval = shared_values ? kval : Num<T>::to_f(kp[(size_t)site.kv_heads * QF_PAGE * D + d]);
                 } else if (d == 0) {
                     atomicOr(err, QF_ERR_NO_PAGE);
                 }
@@ -163,7 +169,13 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
             }
             continue;
         }
-        const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+        float den = l[i], keep = 1.f;
+        if (sinks) {  // the sink's term, on the same maximum as the rest
+            const float m_new = fmaxf(m[i], sinks[h]);
+            keep = expf(m[i] - m_new);
+            den = l[i] * keep + expf(sinks[h] - m_new);
+        }
+        const float inv = den > 0.f ? keep / den : 0.f;
 #pragma unroll
         for (int dd = 0; dd < MAX_DPL; ++dd) {
             const int d = lane + 32 * dd;
@@ -176,7 +188,8 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
 template <typename T>
 __global__ void attention_generic_fold_kernel(T* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                                               const int* __restrict__ slots, int n_heads, int D, int n_chunks, int window,
-                                              const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+                                              const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const float* __restrict__ sinks) {
     const int h = blockIdx.x, seq = blockIdx.y, t = cu_q[seq];
     T* o = out + ((size_t)t * n_heads + h) * D;
     if (slots[seq] < 0) {
@@ -195,14 +208,21 @@ __global__ void attention_generic_fold_kernel(T* __restrict__ out, const int* __
             a = a * alpha + part_o[(row + c) * D + d] * beta;
             m = m_new;
         }
+        if (sinks) {
+            const float m_new = fmaxf(m, sinks[h]);
+            const float alpha = expf(m - m_new);
+            l = l * alpha + expf(sinks[h] - m_new);
+            a = a * alpha;
+        }
         o[d] = Num<T>::from_f(l > 0.f ? a / l : 0.f);
     }
 }
 
-template <typename T>
+template <typename T, int MAX_DPL>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads,
-                  int n_seqs, int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
+                  int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks, int shared_values,
+                  cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (head_dim > 32 * MAX_DPL || kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     const int G = n_heads / kv_heads;
@@ -211,22 +231,22 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     int tokens_per_tile = MAX_ROWS / group_chunk;
     if (tokens_per_tile > max_q_len) tokens_per_tile = max_q_len;
     const size_t smem = (size_t)(MAX_ROWS * head_dim + 2 * KT * (head_dim + 1)) * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, false, MAX_DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     KvSite<T> site{(T*)base, table, page_elems, table_stride, kv_heads, head_dim};
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, kv_heads * chunks, n_seqs);
-    attention_generic_kernel<T, false><<<grid, WARPS * 32, smem, stream>>>((const T*)q, (T*)out, cu_q, tok_pos, slots, site,
-                                                                           n_heads, group_chunk, tokens_per_tile, scale,
-                                                                           window, nullptr, nullptr, err);
+    attention_generic_kernel<T, false, MAX_DPL><<<grid, WARPS * 32, smem, stream>>>(
+        (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, tokens_per_tile, scale, window, nullptr, nullptr,
+        err, sinks, shared_values);
     return (int)cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, int MAX_DPL>
 static int launch_decode(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                          const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads,
                          int n_seqs, int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
-                         cudaStream_t stream) {
+                         const float* sinks, int shared_values, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (head_dim > 32 * MAX_DPL || kv_heads <= 0 || n_heads % kv_heads || max_kv_len <= 0) return (int)cudaErrorInvalidValue;
     const int G = n_heads / kv_heads;
@@ -234,41 +254,63 @@ static int launch_decode(const void* q, void* out, const int* cu_q, const int* t
     const int chunks = (G + group_chunk - 1) / group_chunk;
     const int n_chunks = (max_kv_len + GEN_CHUNK - 1) / GEN_CHUNK;
     const size_t smem = (size_t)(MAX_ROWS * head_dim + 2 * KT * (head_dim + 1)) * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, true, MAX_DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     KvSite<T> site{(T*)base, table, page_elems, table_stride, kv_heads, head_dim};
-    attention_generic_kernel<T, true><<<dim3(n_chunks, kv_heads * chunks, n_seqs), WARPS * 32, smem, stream>>>(
-        (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, 1, scale, window, part_o, part_ml, err);
+    attention_generic_kernel<T, true, MAX_DPL><<<dim3(n_chunks, kv_heads * chunks, n_seqs), WARPS * 32, smem, stream>>>(
+        (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, 1, scale, window, part_o, part_ml, err, nullptr,
+        shared_values);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     attention_generic_fold_kernel<T><<<dim3(n_heads, n_seqs), 64, 0, stream>>>((T*)out, cu_q, tok_pos, slots, n_heads, head_dim,
-                                                                               n_chunks, window, part_o, part_ml);
+                                                                               n_chunks, window, part_o, part_ml, sinks);
     return (int)cudaGetLastError();
 }
 
 // q, out: [n_tokens][n_heads * head_dim]; cu_q: [n_seqs + 1] first token of each sequence in the flat batch;
 // tok_pos: [n_tokens] absolute position of each token; slots: [n_seqs] cache slot of each sequence (-1: padding).
+// sinks: float32 [n_heads] or null; shared_values: the values are the keys (see the top of the file).
+#define QF_GENERIC_DISPATCH(FN, ...)                                                            \
+    if (head_dim <= 32 * MAX_DPL_SMALL)                                                         \
+        return is_bf16 ? FN<bf16, MAX_DPL_SMALL>(__VA_ARGS__) : FN<float, MAX_DPL_SMALL>(__VA_ARGS__); \
+    return is_bf16 ? FN<bf16, MAX_DPL_WIDE>(__VA_ARGS__) : FN<float, MAX_DPL_WIDE>(__VA_ARGS__);
+
+QF_EXPORT int qf_attention_generic_ex(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                      const int* slots, void* base, const int* table, long long page_elems,
+                                      int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                      int max_q_len, float scale, int window, int* err, const float* sinks,
+                                      int shared_values, cudaStream_t stream) {
+    QF_GENERIC_DISPATCH(launch, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                        n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream)
+}
+
 QF_EXPORT int qf_attention_generic(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
                                    const int* slots, void* base, const int* table, long long page_elems,
                                    int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                                    int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
-    return is_bf16 ? launch<bf16>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
-                                  head_dim, n_heads, n_seqs, max_q_len, scale, window, err, stream)
-                   : launch<float>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
-                                   head_dim, n_heads, n_seqs, max_q_len, scale, window, err, stream);
+    return qf_attention_generic_ex(is_bf16, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
+                                   head_dim, n_heads, n_seqs, max_q_len, scale, window, err, nullptr, 0, stream);
 }
 
 // The same for a step of ONE token per sequence, cut into chunks of keys (see the top of the file). `max_kv_len`: an
 // upper bound of any sequence's length after the step; scratch: part_o float32 [n_seqs * n_heads * n_chunks * head_dim],
 // part_ml float32 [n_seqs * n_heads * n_chunks * 2] with n_chunks = ceil(max_kv_len / 256).
+QF_EXPORT int qf_attention_generic_decode_ex(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                             const int* slots, void* base, const int* table, long long page_elems,
+                                             int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                             int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
+                                             const float* sinks, int shared_values, cudaStream_t stream) {
+    QF_GENERIC_DISPATCH(launch_decode, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                        n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err, sinks, shared_values, stream)
+}
+
 QF_EXPORT int qf_attention_generic_decode(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
                                           const int* slots, void* base, const int* table, long long page_elems,
                                           int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                                           int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
                                           cudaStream_t stream) {
-    return is_bf16 ? launch_decode<bf16>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
-                                         head_dim, n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err, stream)
-                   : launch_decode<float>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
-                                          head_dim, n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err, stream);
+    return qf_attention_generic_decode_ex(is_bf16, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride,
+                                          kv_heads, head_dim, n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err,
+                                          nullptr, 0, stream);
 }

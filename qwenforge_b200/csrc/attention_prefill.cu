@@ -11,6 +11,9 @@
 // S = Q K^T and O += P V run on the tensor cores (m16n8k16, bf16 in, float32 accumulate); the online softmax
 // is float32 with base-2 exponentials (the scale folded in). A query at position p sees keys j with
 // max(0, p - window + 1) <= j <= p.
+// `sinks` (float32 per query head, or null): a logit that joins the softmax's denominator once, unscaled, with no key and
+// no value. `shared_values`: the values are the keys themselves (pages of one plane, as a latent attention keeps them):
+// a page is fetched once and read as both.
 #include "mma.cuh"
 
 #define PF_WARPS 4
@@ -21,14 +24,15 @@ template <int D, int G>
 __global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
-                     int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err) {
+                     int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err,
+                     const float* __restrict__ sinks, int shared_values) {
     grid_chain_entry();
     constexpr int LD = D + 8;
     constexpr int KS = D / 16;
     constexpr int NT = D / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][G][64][LD]
-    bf16* v_s = k_s + 2 * G * QF_PAGE * LD;         // [2][G][64][LD]
+    bf16* v_s = shared_values ? k_s : k_s + 2 * G * QF_PAGE * LD;  // [2][G][64][LD]; the keys' own buffer when they are the values
 
     // Which (tile, head, sequence) this block serves. Tiles further down a prompt walk more pages, and the SMs hold
     // several blocks each, so what counts is that the blocks that share an SM have about the same work together:
@@ -101,7 +105,7 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
             for (int i = threadIdx.x; i < QF_PAGE * CH; i += PF_THREADS * G) {
                 const int rr = i / CH, c = (i % CH) * 8;
                 cp_async_16(k_s + (((size_t)buf * G + gi) * QF_PAGE + rr) * LD + c, kp + rr * D + c, held);
-                cp_async_16(v_s + (((size_t)buf * G + gi) * QF_PAGE + rr) * LD + c, vp + rr * D + c, held);
+                if (!shared_values) cp_async_16(v_s + (((size_t)buf * G + gi) * QF_PAGE + rr) * LD + c, vp + rr * D + c, held);
             }
         }
     };
@@ -268,7 +272,13 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
-        const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+        float den = l_run[i], keep = 1.f;
+        if (sinks) {  // the sink's term, in base-2 units like the scores, on a common maximum
+            const float s2 = sinks[head] * 1.4426950408889634f, m_new = fmaxf(m_run[i], s2);
+            keep = exp2f(m_run[i] - m_new);
+            den = l_run[i] * keep + exp2f(s2 - m_new);
+        }
+        const float inv = den > 0.f ? keep / den : 0.f;
         bf16* dst = out + (size_t)(q_begin + row0 + r[i]) * q_width + (size_t)head * D + 2 * (lane & 3);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -278,7 +288,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
 
 template <int D, int G>
 static int launch_groups(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, KvSite<bf16> site,
-                         int n_heads, int n_seqs, int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
+                         int n_heads, int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks,
+                         int shared_values, cudaStream_t stream) {
     size_t smem = (size_t)4 * G * QF_PAGE * (D + 8) * sizeof(bf16);
     const size_t merge = (size_t)(G - 1) * PF_WARPS * (D / 8 * 4 + 4) * 32 * sizeof(float);
     if (smem < merge) smem = merge;
@@ -289,13 +300,14 @@ static int launch_groups(const void* q, void* out, const int* cu_q, const int* t
     if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     return (int)launch_pdl(prefill_flash_kernel<D, G>, dim3((unsigned)blocks), dim3(PF_THREADS * G), smem, stream, (const bf16*)q,
                            (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs, n_tiles, qf_sm_count(),
-                           scale * 1.4426950408889634f, window, err);
+                           scale * 1.4426950408889634f, window, err, sinks, shared_values);
 }
 
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
+                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, const float* sinks,
+                  int shared_values, cudaStream_t stream) {
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     // Two groups of warps per tile when tiles walk many pages and all tiles find room on the SMs at once (a short
     // continuation over a long cache, one prompt of a few thousand tokens): what bounds the kernel then is the longest
@@ -306,24 +318,25 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     const long long tiles = (long long)min((max_q_len + PF_BM - 1) / PF_BM * n_seqs, n_tokens / PF_BM + n_seqs) * n_heads;
     const int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
     const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * (D <= 64 ? 4 : 2);
-    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
-                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
+    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream)
+                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream);
 }
 
 // The arguments of the generic attention kernel, `n_tokens` (the rows of q: all sequences' new tokens) and `max_kv_len`,
 // an upper bound of any sequence's length after this step (both only steer how a tile's pages are shared among warps);
 // bf16 only. cudaErrorInvalidValue for a head size without an
 // instantiation (the caller then uses the generic kernel).
-QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
-                                   void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                   int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
-                                   float scale, int window, int* err, cudaStream_t stream) {
+QF_EXPORT int qf_attention_prefill_ex(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                      void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                      float scale, int window, int* err, const float* sinks, int shared_values,
+                                      cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                 \
     case DIM:                                                                                                        \
         return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
-                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
+                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -333,4 +346,12 @@ QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, co
             return (int)cudaErrorInvalidValue;
     }
 #undef QF_CASE
+}
+
+QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                   void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                   int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                   float scale, int window, int* err, cudaStream_t stream) {
+    return qf_attention_prefill_ex(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                                   n_heads, n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, nullptr, 0, stream);
 }

@@ -19,6 +19,11 @@ typedef __nv_bfloat16 bf16;
 #define QF_ERR_ROW_RANGE 4     // a gathered row index outside the activations
 #define QF_ERR_COPY_TIMEOUT 8  // a bulk copy did not complete within the wait limit
 #define QF_ERR_BARRIER_TIMEOUT 16  // a barrier over the blocks of a persistent kernel was not reached within the wait limit
+#define QF_ERR_POSITION_RANGE 32   // a token's position outside a learned position table
+
+// Rows of a tile of the grouped products (csrc/grouped_gemm.cu); the routing plan (csrc/moe.cu) cuts every expert's
+// rows into tiles of this many.
+#define QF_GROUP_BM 64
 
 template <typename T> struct Num;
 template <> struct Num<float> {

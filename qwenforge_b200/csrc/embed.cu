@@ -18,6 +18,27 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = bad ? 0.f : Num<T>::to_f(row[c]);
 }
 
+// out[t] = table[ids[t]] + positions[tok_pos[t]]: token embedding plus a learned vector per absolute position, summed in
+// float32 (neither is scaled).
+template <typename T>
+__global__ void embed_positions_kernel(const int* __restrict__ ids, const int* __restrict__ tok_pos, const T* __restrict__ table,
+                                       const T* __restrict__ positions, float* __restrict__ out, int vocab, int max_pos,
+                                       int width, int* err) {
+    grid_chain_entry();
+    const int t = blockIdx.x;
+    int id = ids[t], pos = tok_pos[t];
+    const bool bad_id = id < 0 || id >= vocab, bad_pos = pos < 0 || pos >= max_pos;
+    if (threadIdx.x == 0 && bad_id) atomicOr(err, QF_ERR_TOKEN_RANGE);
+    if (threadIdx.x == 0 && bad_pos) atomicOr(err, QF_ERR_POSITION_RANGE);
+    if (bad_id) id = 0;
+    if (bad_pos) pos = 0;
+    const T* row = table + (size_t)id * width;
+    const T* prow = positions + (size_t)pos * width;
+    float* dst = out + (size_t)t * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        dst[c] = (bad_id || bad_pos) ? 0.f : Num<T>::to_f(row[c]) + Num<T>::to_f(prow[c]);
+}
+
 // out[r] = hidden[rows[r]] (+ delta[rows[r]]): the residual stream with its pending update, at the wanted rows.
 template <typename T>
 __global__ void gather_rows_kernel(const float* __restrict__ hidden, const T* __restrict__ delta,
@@ -110,4 +131,18 @@ QF_EXPORT int qf_gather_rows(int is_bf16, const float* hidden, const void* delta
                              int n_out, int n_in, int width, int* err, cudaStream_t stream) {
     return is_bf16 ? gather_launch<bf16>(hidden, delta, rows, out, n_out, n_in, width, err, stream)
                    : gather_launch<float>(hidden, delta, rows, out, n_out, n_in, width, err, stream);
+}
+
+template <typename T>
+static int embed_positions_launch(const int* ids, const int* tok_pos, const void* table, const void* positions, float* out,
+                                  int n_tokens, int vocab, int max_pos, int width, int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    return (int)launch_pdl(embed_positions_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, ids, tok_pos, (const T*)table,
+                           (const T*)positions, out, vocab, max_pos, width, err);
+}
+
+QF_EXPORT int qf_embed_positions(int is_bf16, const int* ids, const int* tok_pos, const void* table, const void* positions,
+                                 float* out, int n_tokens, int vocab, int max_pos, int width, int* err, cudaStream_t stream) {
+    return is_bf16 ? embed_positions_launch<bf16>(ids, tok_pos, table, positions, out, n_tokens, vocab, max_pos, width, err, stream)
+                   : embed_positions_launch<float>(ids, tok_pos, table, positions, out, n_tokens, vocab, max_pos, width, err, stream);
 }

@@ -1,0 +1,207 @@
+// Grouped matrix products: many small products C_g = A_g W_g^T in one launch, each group with a weight of its own.
+//
+// Two ways of saying which rows belong to which group:
+//   uniform  every group takes all `rows` rows and its own slice of columns: A_g = A[:, g * a_group_cols : + K],
+//            C_g = C[:, g * c_group_cols : + N]. This is a product per attention head (a latent attention's queries
+//            taken into the latent space, its latent outputs taken back to value heads).
+//   ragged   the rows are sorted by group and cut into tiles of QF_GROUP_BM rows by a plan on the device (csrc/moe.cu):
+//            tile i belongs to group tile_group[i], starts at row tile_row0[i] and ends where the group's rows end
+//            (offsets[group + 1]). The grid has a block row for every tile that any routing can have; those beyond
+//            n_tiles[0] end at once. This is the experts of a mixture-of-experts feed-forward.
+// W_g = W + g * w_group_stride, row-major [N][K] with leading dimension ldw.
+//
+// bfloat16 runs on the tensor cores (mma.sync m16n8k16, float32 accumulators, cp.async double buffering) when K and all
+// strides are multiples of 8 elements and the bases 16-byte aligned; anything else, and float32, runs a plain tiled
+// kernel in which every output element is one chain of fused multiply-adds over k = 0 .. K-1 (no TF32). In both, a
+// row's result does not depend on which other rows share its tile.
+#include "mma.cuh"
+
+struct GroupedArgs {
+    const void* a;
+    long long lda, a_group_cols;
+    const void* w;
+    long long w_group_stride, ldw;
+    void* c;
+    long long ldc, c_group_cols;
+    int rows, n, k, n_groups;
+    const int* tile_group;   // null: uniform
+    const int* tile_row0;
+    const int* offsets;
+    const int* n_tiles;
+    int max_tiles;
+};
+
+// Which group and which rows this block has; false if it has none.
+__device__ __forceinline__ bool grouped_tile(const GroupedArgs& g, int& group, int& row0, int& row_end) {
+    if (g.tile_group) {
+        if ((int)blockIdx.y >= g.n_tiles[0]) return false;
+        group = g.tile_group[blockIdx.y];
+        row0 = g.tile_row0[blockIdx.y];
+        row_end = min(g.offsets[group + 1], g.rows);
+    } else {
+        group = blockIdx.z;
+        row0 = blockIdx.y * QF_GROUP_BM;
+        row_end = g.rows;
+    }
+    return row0 < row_end;
+}
+
+#define GG_BN 64
+#define GG_BK 16
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+grouped_gemm_plain_kernel(GroupedArgs g) {
+    grid_chain_entry();
+    __shared__ float a_s[GG_BK][QF_GROUP_BM + 1];
+    __shared__ float w_s[GG_BK][GG_BN + 1];
+    int group, m0, m_end;
+    if (!grouped_tile(g, group, m0, m_end)) return;
+    const T* A = (const T*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
+    const T* W = (const T*)g.w + (long long)group * g.w_group_stride;
+    T* C = (T*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int n0 = blockIdx.x * GG_BN;
+    const int N = g.n, K = g.k;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx / GG_BK, k = idx % GG_BK;
+            const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
+            a_s[k][r] = (gm < m_end && gk < K) ? Num<T>::to_f(A[(long long)gm * g.lda + gk]) : 0.f;
+            w_s[k][r] = (gn < N && gk < K) ? Num<T>::to_f(W[(long long)gn * g.ldw + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GG_BK; ++k) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = a_s[k][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = w_s[k][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty + 16 * i;
+        if (gm >= m_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx + 16 * j;
+            if (gn < N) C[(long long)gm * g.ldc + gn] = Num<T>::from_f(acc[i][j]);
+        }
+    }
+}
+
+// bfloat16 on the tensor cores: a block of four warps makes a tile of 64 x 64, warp (wy, wx) its 32 x 32 quarter as
+// 2 x 4 tiles of m16n8k16; both operands arrive in slabs of 32 columns of K by 16-byte asynchronous copies, one slab ahead.
+#define GT_BK 32
+#define GT_LD (GT_BK + 8)
+__global__ void __launch_bounds__(128)
+grouped_gemm_mma_kernel(GroupedArgs g) {
+    grid_chain_entry();
+    __shared__ __align__(16) bf16 a_s[2][QF_GROUP_BM][GT_LD];
+    __shared__ __align__(16) bf16 w_s[2][GG_BN][GT_LD];
+    int group, m0, m_end;
+    if (!grouped_tile(g, group, m0, m_end)) return;
+    const bf16* A = (const bf16*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
+    const bf16* W = (const bf16*)g.w + (long long)group * g.w_group_stride;
+    bf16* C = (bf16*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
+    const int n0 = blockIdx.x * GG_BN, N = g.n, K = g.k;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wy = warp >> 1, wx = warp & 1;
+
+    auto fetch = [&](int k0, int buf) {
+        // 64 rows x 4 chunks of 8 columns for each operand; 128 threads take two chunks of each
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = threadIdx.x + i * 128;
+            const int r = idx >> 2, c = (idx & 3) * 8;
+            const bool k_ok = k0 + c < K;
+            const bool a_ok = k_ok && m0 + r < m_end, w_ok = k_ok && n0 + r < N;
+            cp_async_16(&a_s[buf][r][c], a_ok ? A + (long long)(m0 + r) * g.lda + k0 + c : A, a_ok);
+            cp_async_16(&w_s[buf][r][c], w_ok ? W + (long long)(n0 + r) * g.ldw + k0 + c : W, w_ok);
+        }
+    };
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    fetch(0, 0);
+    cp_async_commit();
+    for (int k0 = 0, turn = 0; k0 < K; k0 += GT_BK, ++turn) {
+        const int buf = turn & 1;
+        if (k0 + GT_BK < K) fetch(k0 + GT_BK, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < GT_BK / 16; ++ks) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) ldmatrix_x4(af[i], &a_s[buf][32 * wy + 16 * i + (lane & 15)][16 * ks + (lane >> 4) * 8]);
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {  // 16 weight rows per ldmatrix.x4
+                uint32_t wf[4];
+                ldmatrix_x4(wf, &w_s[buf][32 * wx + 16 * j2 + (lane >> 4) * 8 + (lane & 7)][16 * ks + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_bf16_16816(acc[i][2 * j2], af[i], wf[0], wf[1]);
+                    mma_bf16_16816(acc[i][2 * j2 + 1], af[i], wf[2], wf[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int gm = m0 + 32 * wy + 16 * i + (lane >> 2) + 8 * half;
+            if (gm >= m_end) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int gn = n0 + 32 * wx + 8 * j + 2 * (lane & 3);
+                bf16* dst = C + (long long)gm * g.ldc + gn;
+                const float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
+                else {
+                    if (gn < N) dst[0] = __float2bfloat16_rn(v0);
+                    if (gn + 1 < N) dst[1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
+static bool mma_takes(const GroupedArgs& g) {
+    const long long strides = g.lda | g.ldw | g.a_group_cols | g.w_group_stride | (long long)g.k;
+    return strides % 8 == 0 && ((uintptr_t)g.a | (uintptr_t)g.w) % 16 == 0;
+}
+
+// See the top of the file. tile_group == null: uniform groups over all rows; else the ragged plan (a_group_cols and
+// c_group_cols are then not used). A, W and C share the activation dtype.
+QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
+                              long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
+                              int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
+                              const int* offsets, const int* n_tiles, int max_tiles, cudaStream_t stream) {
+    if (rows <= 0 || n <= 0 || n_groups <= 0) return 0;
+    GroupedArgs g{a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
+                  tile_group, tile_row0, offsets, n_tiles, max_tiles};
+    const dim3 grid((n + GG_BN - 1) / GG_BN, tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
+    if (grid.y == 0 || grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    if (is_bf16 && mma_takes(g)) return (int)launch_pdl(grouped_gemm_mma_kernel, grid, dim3(128), 0, stream, g);
+    if (is_bf16) return (int)launch_pdl(grouped_gemm_plain_kernel<bf16>, grid, dim3(256), 0, stream, g);
+    return (int)launch_pdl(grouped_gemm_plain_kernel<float>, grid, dim3(256), 0, stream, g);
+}

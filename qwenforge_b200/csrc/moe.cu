@@ -1,0 +1,168 @@
+// Routing of a mixture-of-experts feed-forward, on the device from start to end (no count ever reaches the host, so a
+// step with routed experts replays from a captured graph like any other).
+//
+//   plan     from the router's float32 logits [tokens][experts]: per token the `top` experts with the largest
+//            score, the score being sigmoid(logit) or, with `softmax_scores`, the softmax over the experts; the weights
+//            are the chosen scores, divided by their sum when `renormalize` is set. The (token, expert) pairs are
+//            sorted by expert: rows offsets[e] .. offsets[e+1]-1 of the sorted order belong to expert e, and every
+//            expert's rows are cut into tiles of QF_GROUP_BM rows for the grouped product (csrc/grouped_gemm.cu).
+//   gather   x_sorted[r] = x[token of r] (* weight of r, when the weight multiplies the expert's input)
+//   combine  out[t] = sum over the token's pairs, in the order of its choice, of y_sorted[row of the pair]
+//            (* weight, when the weight multiplies the expert's output), summed in float32
+//
+// One block makes the plan: the work is a few values per token. The order of an expert's rows among themselves is
+// whatever the block's atomics gave; no result depends on it, since a row of a product is computed alone.
+#include <float.h>
+
+#include "common.cuh"
+
+#define MOE_PLAN_THREADS 1024
+#define MOE_MAX_TOP 16
+
+// Scratch in pair order (pair = token * top + k): pair_expert, pair_weight. Results: dest [pairs] (the row of every pair),
+// and in row order sorted_token [pairs], sorted_weight float32 [pairs]; offsets [experts + 1]; tile_group, tile_row0
+// [max_tiles]; n_tiles [1].
+__global__ void __launch_bounds__(MOE_PLAN_THREADS)
+moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ sorted_token,
+                float* __restrict__ sorted_weight, int* __restrict__ dest, int* __restrict__ offsets,
+                int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles) {
+    grid_chain_entry();
+    extern __shared__ int shared[];
+    int* counts = shared;                   // [experts]: rows per expert, then every expert's first row
+    int* first_tile = shared + n_experts;   // [experts + 1]
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    // pass 1: choose, and take a rank among the expert's rows
+    for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
+        const float* z = logits + (size_t)t * n_experts;
+        float top_z = -FLT_MAX, denom = 1.f;
+        if (softmax_scores) {
+            for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z[e]);
+            denom = 0.f;
+            for (int e = 0; e < n_experts; ++e) denom += expf(z[e] - top_z);
+        }
+        int chosen[MOE_MAX_TOP];
+        float weight[MOE_MAX_TOP], total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float best_z = -FLT_MAX;
+            for (int e = 0; e < n_experts; ++e) {
+                bool taken = false;
+                for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
+                if (!taken && (best < 0 || z[e] > best_z)) {   // the larger logit is the larger score; ties go to the lower index
+                    best = e;
+                    best_z = z[e];
+                }
+            }
+            chosen[k] = best;
+            weight[k] = softmax_scores ? expf(best_z - top_z) / denom : 1.0f / (1.0f + expf(-best_z));
+            total += weight[k];
+        }
+        for (int k = 0; k < top; ++k) {
+            const int pair = t * top + k;
+            pair_expert[pair] = chosen[k];
+            dest[pair] = atomicAdd(&counts[chosen[k]], 1);        // for now: the pair's rank among its expert's rows
+            pair_weight[pair] = renormalize ? weight[k] / total : weight[k];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0, tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            const int n = counts[e];
+            offsets[e] = row;
+            counts[e] = row;
+            first_tile[e] = tile;
+            row += n;
+            tile += (n + QF_GROUP_BM - 1) / QF_GROUP_BM;
+        }
+        offsets[n_experts] = row;
+        first_tile[n_experts] = tile;
+        n_tiles[0] = tile < max_tiles ? tile : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int row0 = counts[e];
+        for (int i = first_tile[e]; i < first_tile[e + 1] && i < max_tiles; ++i) {
+            tile_group[i] = e;
+            tile_row0[i] = row0 + (i - first_tile[e]) * QF_GROUP_BM;
+        }
+    }
+    // pass 2: every pair's row (each thread finishes the pairs it made itself)
+    for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
+        for (int k = 0; k < top; ++k) {
+            const int pair = t * top + k;
+            const int row = counts[pair_expert[pair]] + dest[pair];
+            dest[pair] = row;
+            sorted_token[row] = t;
+            sorted_weight[row] = pair_weight[pair];
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ sorted_token, const float* __restrict__ sorted_weight,
+                  T* __restrict__ out, int n_rows, int width, int scale_input) {
+    grid_chain_entry();
+    const int r = blockIdx.x;
+    if (r >= n_rows) return;
+    const T* src = x + (size_t)sorted_token[r] * width;
+    const float w = scale_input ? sorted_weight[r] : 1.f;
+    T* dst = out + (size_t)r * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = Num<T>::from_f(Num<T>::to_f(src[c]) * w);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const float* __restrict__ sorted_weight,
+                   T* __restrict__ out, int n_tokens, int top, int width, int scale_output) {
+    grid_chain_entry();
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = dest[t * top + k];
+            const float v = Num<T>::to_f(y[(size_t)row * width + c]);
+            sum += scale_output ? v * sorted_weight[row] : v;
+        }
+        out[(size_t)t * width + c] = Num<T>::from_f(sum);
+    }
+}
+
+// The most tiles any routing of `pairs` rows over `n_experts` experts can have.
+QF_EXPORT int qf_moe_max_tiles(int pairs, int n_experts) { return (pairs + QF_GROUP_BM - 1) / QF_GROUP_BM + n_experts; }
+
+// pairs = n_tokens * top: pair_expert, pair_weight (scratch), sorted_token, sorted_weight and dest have that many elements.
+QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                          int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                          int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+    return (int)launch_pdl(moe_plan_kernel, dim3(1), dim3(MOE_PLAN_THREADS), smem, stream, logits, n_tokens, n_experts, top,
+                           softmax_scores, renormalize, pair_expert, pair_weight, sorted_token, sorted_weight, dest, offsets,
+                           tile_group, tile_row0, n_tiles, max_tiles);
+}
+
+QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token, const float* sorted_weight, void* out,
+                            int n_rows, int width, int scale_input, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (is_bf16)
+        return (int)launch_pdl(moe_gather_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, (const bf16*)x, sorted_token,
+                               sorted_weight, (bf16*)out, n_rows, width, scale_input);
+    return (int)launch_pdl(moe_gather_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)x, sorted_token,
+                           sorted_weight, (float*)out, n_rows, width, scale_input);
+}
+
+QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
+                             int top, int width, int scale_output, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (is_bf16)
+        return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)y, dest, sorted_weight,
+                               (bf16*)out, n_tokens, top, width, scale_output);
+    return (int)launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)y, dest, sorted_weight,
+                           (float*)out, n_tokens, top, width, scale_output);
+}

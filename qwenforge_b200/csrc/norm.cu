@@ -172,3 +172,71 @@ QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, lon
         return (int)launch_pdl(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, hidden, (const bf16*)delta, n);
     return (int)launch_pdl(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, hidden, (const float*)delta, n);
 }
+
+// A sublayer's output normalised on its way into the stream, and the stream normalised again for the next sublayer:
+//   hidden += y * rsqrt(mean(y^2) + eps_post) * post_weight;   out = hidden * rsqrt(mean(hidden^2) + eps_next) * next_weight
+// (the second half only when next_weight is given). Both sums of squares, both roots and the addition are float32. A block
+// per row; a thread keeps up to SW_KEEP of the row's elements in registers between the passes, wider rows are read again.
+#define SW_KEEP 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
+                     const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int width) {
+    grid_chain_entry();
+    __shared__ float scratch[33];
+    float* h = hidden + (size_t)blockIdx.x * width;
+    const T* yr = y + (size_t)blockIdx.x * width;
+    float kept[SW_KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < SW_KEEP; ++u) {
+        const int c = threadIdx.x + u * 256;
+        kept[u] = c < width ? Num<T>::to_f(yr[c]) : 0.f;
+        ss += kept[u] * kept[u];
+    }
+    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
+        const float v = Num<T>::to_f(yr[c]);
+        ss += v * v;
+    }
+    const float inv_y = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_post);
+    ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < SW_KEEP; ++u) {
+        const int c = threadIdx.x + u * 256;
+        if (c < width) {
+            kept[u] = h[c] + kept[u] * inv_y * Num<T>::to_f(post_weight[c]);
+            h[c] = kept[u];
+            ss += kept[u] * kept[u];
+        }
+    }
+    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
+        const float v = h[c] + Num<T>::to_f(yr[c]) * inv_y * Num<T>::to_f(post_weight[c]);
+        h[c] = v;
+        ss += v * v;
+    }
+    if (!next_weight) return;
+    const float inv_h = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_next);
+    T* o = out + (size_t)blockIdx.x * width;
+#pragma unroll
+    for (int u = 0; u < SW_KEEP; ++u) {
+        const int c = threadIdx.x + u * 256;
+        if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * Num<T>::to_f(next_weight[c]));
+    }
+    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256)   // each thread re-reads the columns it wrote itself
+        o[c] = Num<T>::from_f(h[c] * inv_h * Num<T>::to_f(next_weight[c]));
+}
+
+template <typename T>
+static int sandwich_launch(float* hidden, const void* y, const void* post_weight, float eps_post, const void* next_weight,
+                           float eps_next, void* out, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    return (int)launch_pdl(sandwich_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y, (const T*)post_weight,
+                           eps_post, (const T*)next_weight, eps_next, (T*)out, width);
+}
+
+// y, post_weight, next_weight (may be null) and out (null with it) share a dtype; hidden is float32 [rows, width].
+QF_EXPORT int qf_sandwich_norm(int is_bf16, float* hidden, const void* y, const void* post_weight, float eps_post,
+                               const void* next_weight, float eps_next, void* out, int rows, int width, cudaStream_t stream) {
+    return is_bf16 ? sandwich_launch<bf16>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, stream)
+                   : sandwich_launch<float>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, stream);
+}

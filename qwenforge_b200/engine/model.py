@@ -17,6 +17,7 @@ from ..cache import SequenceCache
 from ..config import ModelConfig, ModelSpec, load_config, resolve_dtype
 from ..csrc import prepare
 from ..parts import build_block, build_part
+from ..parts.base import PendingNormed
 from ..weights import load_weights, random_state_on_device
 from .step import StepContext, context_of, pack_step
 
@@ -97,7 +98,8 @@ class Model:
         resolved = resolve_dtype(dtype, getattr(config, "torch_dtype", None))
         model = cls(config.model_spec(), resolved, device, attention)
         model.config = config
-        tensors = load_weights(model_dir, model.tensor_specs(), resolved, model.device, model.spec.redundant_tensors)
+        tensors = load_weights(model_dir, model.tensor_specs(), resolved, model.device, model.spec.redundant_tensors,
+                               model.spec.ignored_tensors)
         return model.bind(tensors)
 
     @classmethod
@@ -126,11 +128,18 @@ class Model:
         for index, entry in enumerate(self.spec.schedule):
             own = entry.cache_from is None
             site = cache.site(index if own else entry.cache_from)
-            delta = self.blocks[entry.layer].forward(hidden, delta, ctx, site, own)
+            block = self.blocks[entry.layer]
+            if isinstance(delta, PendingNormed) and not getattr(block, "accepts_pending_normed", False):
+                delta.add_to(hidden)
+                delta = None
+            delta = block.forward(hidden, delta, ctx, site, own)
             if self.observer is not None:
-                self.observer(index + 1, hidden, delta)
+                self.observer(index + 1, hidden, delta.value() if isinstance(delta, PendingNormed) else delta)
         if ctx.want_rows is None:
             return None
+        if isinstance(delta, PendingNormed):
+            delta.add_to(hidden)
+            delta = None
         shape = (ctx.want_rows.numel(), hidden.shape[1])
         rms = self.final_norm.fused_rms()
         if rms is not None and (delta is None or delta.dtype == rms[0].dtype):

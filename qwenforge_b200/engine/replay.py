@@ -10,8 +10,8 @@ Steps come on standard input, one JSON object a line:
 names requests that are finished after the step (their cache slot and pages are given back). For a step
 that wants something, `<out>/<step>.f32` receives the logits at the wanted places, in the order of the
 entries and of `want`, as little-endian float32 [wanted, vocab]. After every step `done <step>` is
-printed and flushed. `--max-tokens` is the most tokens live requests hold at any time, each request's
-count rounded up to the cache's page of 64; it sizes the cache.
+printed and flushed. `--max-tokens` is the most tokens live requests hold at any time; it sizes the cache, which adds
+a page of 64 for every request that can be live (each request's last page is partly empty).
 
 `--dump-layers DIR` also writes, for every step, the residual stream of the step's tokens after the embedding
 (`DIR/<step>.layer0.f32`) and after every schedule entry k (`DIR/<step>.layer<k+1>.f32`), float32 [tokens, width]:
@@ -40,7 +40,7 @@ def parse_args(argv=None):
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder that receives <step>.f32")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time (each rounded up to 64)")
+                   help="most tokens live requests hold at any time")
     p.add_argument("--dump-layers", default=None, metavar="DIR",
                    help="also write the residual stream after the embedding and after every schedule entry")
     p.add_argument("--device", default="cuda")
@@ -90,8 +90,10 @@ def main(argv=None) -> int:
     attention = "auto" if args.attn_implementation.lower() in ("sdpa", "flash", "auto") else "generic"
     with torch.inference_mode():
         model = Model.from_dir(args.model, args.dtype, args.device, attention)
-        n_tokens = round_up(max(args.max_tokens, 1), PAGE_TOKENS)
-        cache = model.new_cache(n_tokens, max_seqs=min(n_tokens // PAGE_TOKENS, 4096))
+        # every live request may leave its last page partly empty: one page more per slot
+        max_seqs = min(max(args.max_tokens, 1), 1024)
+        n_tokens = round_up(max(args.max_tokens, 1), PAGE_TOKENS) + max_seqs * PAGE_TOKENS
+        cache = model.new_cache(n_tokens, max_seqs=max_seqs)
         dump_dir = Path(args.dump_layers) if args.dump_layers else None
         if dump_dir is not None:
             dump_dir.mkdir(parents=True, exist_ok=True)

@@ -25,6 +25,7 @@ ERR_NO_PAGE = 2
 ERR_ROW_RANGE = 4
 ERR_COPY_TIMEOUT = 8
 ERR_BARRIER_TIMEOUT = 16
+ERR_POSITION_RANGE = 32
 
 _ERROR_TEXT = {
     ERR_TOKEN_RANGE: "a token id lies outside the embedding table",
@@ -32,6 +33,7 @@ _ERROR_TEXT = {
     ERR_ROW_RANGE: "a wanted row lies outside the step's tokens",
     ERR_COPY_TIMEOUT: "a bulk copy into shared memory did not complete within its wait limit",
     ERR_BARRIER_TIMEOUT: "the blocks of a persistent kernel did not all reach a barrier within its wait limit",
+    ERR_POSITION_RANGE: "a token's position lies outside the learned position table",
 }
 
 
@@ -229,13 +231,17 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
 
 
 GENERIC_DECODE_CHUNK = 256
+GENERIC_MAX_HEAD_DIM = 512
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
                       window: int, err: torch.Tensor, scratch: Optional["DecodeScratch"] = None,
-                      max_kv_len: Optional[int] = None) -> None:
+                      max_kv_len: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
+                      shared_values: bool = False) -> None:
     """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math).
+    `sinks` (float32 [n_heads]): a logit per head that joins the softmax's denominator once, with no key and no value.
+    `shared_values`: the values are the keys themselves (a cache whose pages hold one plane).
     A step of one token per sequence whose longest sequence exceeds one chunk of 256 keys is cut into chunks of keys
     when `scratch` and `max_kv_len` (a bound on any sequence's length after the step) are given: a block per chunk,
     then a fold in rising order; which chunks a row has depends on its own position only."""
@@ -243,24 +249,29 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
     _dev("out", out, q.dtype)
     _dev("cache", site.storage, q.dtype)
     d = site.head_dim
-    if d > 256:
-        raise KernelError(f"attention_generic: head_dim {d} > 256 is not supported")
+    if d > GENERIC_MAX_HEAD_DIM:
+        raise KernelError(f"attention_generic: head_dim {d} > {GENERIC_MAX_HEAD_DIM} is not supported")
     if q.shape[1] != n_heads * d or out.shape != q.shape:
         raise KernelError("attention_generic: q/out widths do not match the head count")
+    if sinks is not None:
+        _dev("sinks", sinks, torch.float32)
+        if sinks.numel() != n_heads:
+            raise KernelError("attention_generic: sinks must hold one float32 per query head")
     if (scratch is not None and max_kv_len is not None and max_q_len == 1 and q.shape[0] == n_seqs
             and max_kv_len > GENERIC_DECODE_CHUNK):
         n_chunks = -(-int(max_kv_len) // GENERIC_DECODE_CHUNK)
         scratch.ensure(n_seqs, n_heads, n_chunks, d, 0)
-        _check(library("attention_generic").qf_attention_generic_decode(
+        _check(library("attention_generic").qf_attention_generic_decode_ex(
             _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
             _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
             _I(n_seqs), _I(int(max_kv_len)), _F(scale), _I(window), _ptr(scratch.part_o), _ptr(scratch.part_ml), _ptr(err),
-            _stream()), "attention_generic")
+            _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_generic")
         return
-    _check(library("attention_generic").qf_attention_generic(
+    _check(library("attention_generic").qf_attention_generic_ex(
         _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
         _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
-        _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _stream()), "attention_generic")
+        _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _ptr(sinks), _I(int(bool(shared_values))), _stream()),
+        "attention_generic")
 
 
 FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
@@ -268,8 +279,10 @@ FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
-                      window: int, err: torch.Tensor, max_kv_len: Optional[int] = None) -> None:
+                      window: int, err: torch.Tensor, max_kv_len: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
     """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128.
+    `sinks`, `shared_values`: as in `attention_generic`.
     `max_kv_len`: an upper bound of any sequence's length after the step (None: unknown, taken as long); it only
     steers whether a tile of rows shares its pages among two groups of warps."""
     _dev("q", q, torch.bfloat16)
@@ -281,11 +294,15 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
                           "use attention_generic")
     if q.shape[1] != n_heads * d or out.shape != q.shape:
         raise KernelError("attention_prefill: q/out widths do not match the head count")
-    _check(library("attention_prefill").qf_attention_prefill(
+    if sinks is not None:
+        _dev("sinks", sinks, torch.float32)
+        if sinks.numel() != n_heads:
+            raise KernelError("attention_prefill: sinks must hold one float32 per query head")
+    _check(library("attention_prefill").qf_attention_prefill_ex(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
-        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()),
-        "attention_prefill")
+        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err),
+        _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_prefill")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)
@@ -374,13 +391,18 @@ def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torc
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, scale: float, window: int,
                      n_splits: int, scratch: DecodeScratch, err: torch.Tensor, plan: Optional[torch.Tensor] = None,
-                     fold_later: bool = False) -> None:
+                     fold_later: bool = False, sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
     """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128.
     `n_splits` is the most blocks that share one (sequence, kv head); `plan` (attention_decode_plan with the same
     shape, made in this step; made here when absent) says how many of them each sequence gets. With `fold_later` the
     kernel stops at the runs' partial results in `scratch` and writes no `out` (which may be None): `fold_project`
-    folds them on its way into the output projection."""
+    folds them on its way into the output projection. `sinks`, `shared_values`: as in `attention_generic` (sinks not
+    with `fold_later`)."""
     _dev("q", q, torch.bfloat16)
+    if sinks is not None:
+        _dev("sinks", sinks, torch.float32)
+        if sinks.numel() != n_heads or fold_later:
+            raise KernelError("attention_decode: sinks must hold one float32 per query head, and do not go with fold_later")
     if not fold_later:
         _dev("out", out, torch.bfloat16)
     _dev("cache", site.storage, torch.bfloat16)
@@ -399,12 +421,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok
     partials = n_splits > 1 or fold_later
     if partials:
         scratch.ensure(n_seqs, n_heads, n_splits, d, n_counters)
-    _check(library("attention_decode").qf_attention_decode(
+    _check(library("attention_decode").qf_attention_decode_ex(
         _ptr(q), _ptr(None if fold_later else out), _ptr(cu_q), _ptr(plan), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _F(scale),
         _I(window), _I(n_splits), _I(1 if fold_later else 0), _ptr(scratch.part_o if partials else None),
         _ptr(scratch.part_ml if partials else None), _ptr(scratch.counters if partials else None), _ptr(err),
-        _stream()), "attention_decode")
+        _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_decode")
 
 
 class _FoldProjectArgs(ctypes.Structure):
@@ -944,3 +966,185 @@ def tc_gemm(epilogue: int, x: torch.Tensor, weight: torch.Tensor, out: torch.Ten
     if code == 801:
         raise KernelError("tc_gemm: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
     _check(code, "tc_gemm")
+
+
+# ---------------------------------------------------------------------------------------------- parts of other designs
+
+def embed_positions(ids: torch.Tensor, tok_pos: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+                    out: torch.Tensor, err: torch.Tensor) -> None:
+    """out[t] = float32(table[ids[t]]) + float32(positions[tok_pos[t]]): a token embedding plus a learned vector per
+    absolute position. ids, tok_pos int32 [T]; table [V, W], positions [P, W] of one dtype; out float32 [T, W]."""
+    _dev("ids", ids, torch.int32)
+    _dev("tok_pos", tok_pos, torch.int32)
+    _dev("table", table)
+    _dev("positions", positions, table.dtype)
+    _dev("out", out, torch.float32)
+    n, (vocab, width) = ids.numel(), table.shape
+    if out.shape != (n, width) or positions.shape[1] != width or tok_pos.numel() != n:
+        raise KernelError("embed_positions: out must be [tokens, width], positions [places, width]")
+    _check(library("embed").qf_embed_positions(_I(_is_bf16(table.dtype)), _ptr(ids), _ptr(tok_pos), _ptr(table),
+                                               _ptr(positions), _ptr(out), _I(n), _I(vocab), _I(positions.shape[0]),
+                                               _I(width), _ptr(err), _stream()), "embed_positions")
+
+
+def sandwich_norm(hidden: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
+                  next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                  out: Optional[torch.Tensor] = None) -> None:
+    """hidden += rmsnorm(y) * post_weight; then, if `next_weight` is given, out = rmsnorm(hidden) * next_weight: a
+    sublayer's output normalised on its way into the float32 stream, and the stream normalised for the next sublayer, in
+    one pass. y, the weights and out share a dtype."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("y", y)
+    _dev("post_weight", post_weight, y.dtype)
+    rows, width = hidden.shape
+    if y.shape != hidden.shape or post_weight.numel() != width:
+        raise KernelError("sandwich_norm: y must have the stream's shape and post_weight its width")
+    if next_weight is not None:
+        _dev("next_weight", next_weight, y.dtype)
+        _dev("out", out, y.dtype)
+        if out.shape != hidden.shape or next_weight.numel() != width:
+            raise KernelError("sandwich_norm: out must have the stream's shape and next_weight its width")
+    _check(library("norm").qf_sandwich_norm(_I(_is_bf16(y.dtype)), _ptr(hidden), _ptr(y), _ptr(post_weight), _F(post_eps),
+                                            _ptr(next_weight), _F(next_eps), _ptr(out if next_weight is not None else None),
+                                            _I(rows), _I(width), _stream()), "sandwich_norm")
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, out: torch.Tensor) -> None:
+    """out[t, i] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate_up[t, i], limit), u = clamp(gate_up[t, I + i], -limit, limit)."""
+    _dev("gate_up", gate_up)
+    _dev("out", out, gate_up.dtype)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2):
+        raise KernelError("clamped_glu: out must be [rows, width / 2]")
+    _check(library("activation").qf_clamped_glu(_I(_is_bf16(gate_up.dtype)), _ptr(gate_up), _ptr(out), _I(rows),
+                                                _I(two_i // 2), _F(limit), _F(alpha), _stream()), "clamped_glu")
+
+
+def latent_norm_cache(down: torch.Tensor, q_rank: int, q_norm: Optional[torch.Tensor], kv_norm: torch.Tensor, eps: float,
+                      tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, q_latent: Optional[torch.Tensor],
+                      site: KvSiteArgs, write_cache: bool, err: torch.Tensor,
+                      latent_out: Optional[torch.Tensor] = None) -> None:
+    """The two latents of a latent attention from their fused down-projection `down` (float32 [T, q_rank + kv_rank]):
+    q_latent [T, q_rank] = rmsnorm(down[:, :q_rank]) * q_norm, and rmsnorm(down[:, q_rank:]) * kv_norm written to each
+    token's own position in a one-plane cache of a single head of kv_rank elements (`site`; and to `latent_out` in token
+    order, if given). q_rank 0: no query latent."""
+    _dev("down", down, torch.float32, contiguous=False)
+    _dev("kv_norm", kv_norm)
+    _dev("cache", site.storage, kv_norm.dtype)
+    for name, t in (("tok_seq", tok_seq), ("tok_pos", tok_pos), ("slots", slots)):
+        _dev(name, t, torch.int32)
+    n, kv_rank = down.shape[0], site.head_dim
+    if down.stride(1) != 1 or down.shape[1] != q_rank + kv_rank or site.kv_heads != 1 or kv_norm.numel() != kv_rank:
+        raise KernelError("latent_norm_cache: down must be [tokens, q_rank + kv_rank] and the cache hold one head of kv_rank")
+    if q_rank:
+        _dev("q_norm", q_norm, kv_norm.dtype)
+        _dev("q_latent", q_latent, kv_norm.dtype)
+        if q_latent.shape != (n, q_rank) or q_norm.numel() != q_rank:
+            raise KernelError("latent_norm_cache: q_latent must be [tokens, q_rank]")
+    if latent_out is not None:
+        _dev("latent_out", latent_out, kv_norm.dtype)
+        if latent_out.shape != (n, kv_rank):
+            raise KernelError("latent_norm_cache: latent_out must be [tokens, kv_rank]")
+    _check(library("latent_cache").qf_latent_norm_cache(
+        _I(_is_bf16(kv_norm.dtype)), _ptr(down), _I(down.stride(0)), _I(q_rank), _I(kv_rank), _ptr(q_norm if q_rank else None),
+        _ptr(kv_norm), _F(eps), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(q_latent if q_rank else None),
+        _ptr(latent_out), _ptr(site.storage), _ptr(site.table), _LL(site.page_elems), _I(site.table_stride),
+        _I(1 if write_cache else 0), _I(n), _ptr(err), _stream()), "latent_norm_cache")
+
+
+def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan) -> None:
+    groups, n, k = weight.shape
+    _check(library("grouped_gemm").qf_grouped_gemm(
+        _I(_is_bf16(x.dtype)), _ptr(x), _LL(x.stride(0)), _LL(a_group_cols), _ptr(weight), _LL(weight.stride(0)),
+        _LL(weight.stride(1)), _ptr(out), _LL(out.stride(0)), _LL(c_group_cols), _I(rows), _I(n), _I(k), _I(groups),
+        _ptr(plan.tile_group if plan else None), _ptr(plan.tile_row0 if plan else None), _ptr(plan.offsets if plan else None),
+        _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _stream()), "grouped_gemm")
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """A product per head in one launch: out[:, g*N:(g+1)*N] = x[:, g*K:(g+1)*K] @ weight[g].T for weight [G, N, K],
+    x [T, G*K], out [T, G*N], all of the activation dtype."""
+    _dev("x", x, None, contiguous=False)
+    _dev("weight", weight, x.dtype, contiguous=False)
+    _dev("out", out, x.dtype, contiguous=False)
+    groups, n, k = weight.shape
+    if x.shape[1] != groups * k or out.shape != (x.shape[0], groups * n) or weight.stride(2) != 1 or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"head_linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
+    _grouped(x, weight, out, k, n, x.shape[0], None)
+
+
+GROUP_TILE_ROWS = 64   # rows of a tile of the grouped products (QF_GROUP_BM in csrc/common.cuh)
+
+
+class MoePlan:
+    """One routing of a step's tokens over experts, on the device (csrc/moe.cu): `top` (token, expert) pairs per token,
+    sorted by expert into rows. dest[t * top + j]: the row of token t's j-th choice; sorted_token / sorted_weight: each row's
+    token and routing weight; offsets: every expert's first row; tile_*: the rows cut into tiles for `expert_linear`."""
+
+    def __init__(self, n_tokens: int, n_experts: int, top: int, device):
+        self.n_tokens, self.n_experts, self.top = n_tokens, n_experts, top
+        self.pairs = pairs = n_tokens * top
+        self.max_tiles = -(-pairs // GROUP_TILE_ROWS) + n_experts   # the most tiles any routing can have
+        ints = torch.empty(3 * pairs + n_experts + 1 + 2 * self.max_tiles + 1, dtype=torch.int32, device=device)
+        floats = torch.empty(2 * pairs, dtype=torch.float32, device=device)
+        o = 0
+
+        def take(count):
+            nonlocal o
+            piece = ints[o:o + count]
+            o += count
+            return piece
+
+        self.pair_expert, self.sorted_token, self.dest = take(pairs), take(pairs), take(pairs)
+        self.offsets, self.tile_group, self.tile_row0, self.n_tiles = take(n_experts + 1), take(self.max_tiles), take(self.max_tiles), take(1)
+        self.pair_weight, self.sorted_weight = floats[:pairs], floats[pairs:]
+
+
+def moe_plan(logits: torch.Tensor, top: int, softmax_scores: bool = False, renormalize: bool = False) -> MoePlan:
+    """Route: logits float32 [T, E] -> the `top` experts with the largest scores per token (sigmoid of the logit, or the
+    softmax over the experts) and the sorted rows (see `MoePlan`). Everything stays on the device."""
+    _dev("logits", logits, torch.float32)
+    n_tokens, n_experts = logits.shape
+    plan = MoePlan(n_tokens, n_experts, top, logits.device)
+    code = library("moe").qf_moe_plan(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
+                                      _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
+                                      _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),
+                                      _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles), _stream())
+    if code == 1:
+        raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16, experts <= 8192)")
+    _check(code, "moe_plan")
+    return plan
+
+
+def moe_gather(x: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_input: bool) -> None:
+    """out[row] = x[token of the row] (times the row's routing weight with `scale_input`); out [T * top, W]."""
+    _dev("x", x)
+    _dev("out", out, x.dtype)
+    if out.shape != (plan.pairs, x.shape[1]) or x.shape[0] != plan.n_tokens:
+        raise KernelError("moe_gather: out must be [tokens * top, width]")
+    _check(library("moe").qf_moe_gather(_I(_is_bf16(x.dtype)), _ptr(x), _ptr(plan.sorted_token), _ptr(plan.sorted_weight),
+                                        _ptr(out), _I(plan.pairs), _I(x.shape[1]), _I(int(scale_input)), _stream()), "moe_gather")
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output: bool) -> None:
+    """out[t] = the sum over token t's choices, in their order, of y[row of the choice] (times the routing weight with
+    `scale_output`), summed in float32; y [T * top, W], out [T, W]."""
+    _dev("y", y)
+    _dev("out", out, y.dtype)
+    if y.shape[0] != plan.pairs or out.shape != (plan.n_tokens, y.shape[1]):
+        raise KernelError("moe_combine: y must be [tokens * top, width], out [tokens, width]")
+    _check(library("moe").qf_moe_combine(_I(_is_bf16(y.dtype)), _ptr(y), _ptr(plan.dest), _ptr(plan.sorted_weight), _ptr(out),
+                                         _I(plan.n_tokens), _I(plan.top), _I(y.shape[1]), _I(int(scale_output)), _stream()),
+           "moe_combine")
+
+
+def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor) -> None:
+    """out[row] = x[row] @ weight[expert of the row].T for rows sorted by expert (`plan`): x [T * top, K], weight [E, N, K],
+    out [T * top, N], all of the activation dtype; one launch, no count on the host."""
+    _dev("x", x)
+    _dev("weight", weight, x.dtype)
+    _dev("out", out, x.dtype)
+    groups, n, k = weight.shape
+    if groups != plan.n_experts or x.shape != (plan.pairs, k) or out.shape != (plan.pairs, n):
+        raise KernelError(f"expert_linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
+    _grouped(x, weight, out, 0, 0, plan.pairs, plan)

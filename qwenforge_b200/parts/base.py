@@ -43,10 +43,12 @@ from ..config.spec import PartSpec
 class TensorSpec:
     """One tensor of the weight files.
 
-    init  how the random-weights mode draws it: "matrix" N(0, 0.02), "bias" N(0, 0.02), "norm" 1 + N(0, 0.1)
+    init  how the random-weights mode draws it: "matrix" N(0, 0.02), "bias" N(0, 0.02), "norm" 1 + N(0, 0.1),
+          "logit" N(0, 1)
     keep  "compute": kept in the activation dtype (bfloat16, or float32 on the 32-bit path)
           "stored":  kept as the file stores it if that is a 32-bit float, else as "compute"
           "int32":   an integer table, kept as int32
+          "float32": kept as float32 in both precisions
     fallback  another tensor name that stands in when the files do not hold `name` (a head that
               shares the embedding table in files that say nothing about tying)
     """
@@ -89,6 +91,25 @@ class Part:
         """The bound tensors that every step reads in full (for the measurement's byte counts); tables that a step
         only gathers rows from are not among them."""
         return []
+
+
+class PendingNormed:
+    """A sublayer's output that still has to be normalised (RMS, weight, eps) and added to the residual stream: what a
+    block with norms after its sublayers hands to whoever runs next, so that the addition rides on that part's first norm
+    kernel (`ops.sandwich_norm`). The model resolves it itself before anything that only knows plain deltas."""
+    __slots__ = ("y", "weight", "eps")
+
+    def __init__(self, y: torch.Tensor, weight: torch.Tensor, eps: float):
+        self.y, self.weight, self.eps = y, weight, eps
+
+    def add_to(self, hidden: torch.Tensor) -> None:
+        from .. import ops
+        ops.sandwich_norm(hidden, self.y, self.weight, self.eps)
+
+    def value(self) -> torch.Tensor:
+        """The float32 tensor that will be added (for diagnosis; not on the product path)."""
+        y = self.y.to(torch.float32)
+        return y * torch.rsqrt(y.square().mean(-1, keepdim=True) + self.eps) * self.weight.to(torch.float32)
 
 
 class Embedding(Part):

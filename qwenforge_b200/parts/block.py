@@ -5,7 +5,10 @@ The stream `hidden` is float32 and is updated in place; a part's output (`delta`
 the *next* norm's kernel, so a block takes the pending delta of the layer before it and returns its own."""
 from __future__ import annotations
 
-from .base import Part
+import torch
+
+from .. import ops
+from .base import Norm, Part, PendingNormed
 from .registry import build_part, register_part
 
 
@@ -41,4 +44,52 @@ class PreNormBlock(Part):
         return self.feed_forward.forward(x, ctx)
 
 
+class SandwichBlock(Part):
+    """Norms before AND after each sublayer:  h += post_1(mixer(norm_1(h)));  h += post_2(feed_forward(norm_2(h))).
+    Reads the layer spec's parts `mixer_norm`, `mixer`, `mixer_post_norm` and, if the layer has a feed-forward,
+    `feed_forward_norm`, `feed_forward`, `feed_forward_post_norm`. The norms after the sublayers must be plain RMS norms
+    (`fused_rms`): each rides, with its addition into the stream, on the kernel of the norm that follows it
+    (`ops.sandwich_norm`), the last one of a layer on the first norm of the next layer."""
+
+    accepts_pending_normed = True
+
+    def __init__(self, layer_spec):
+        self.kind = "sandwich_norm"
+        self.mixer_norm = build_part("norm", layer_spec.part("mixer_norm"))
+        self.mixer = build_part("mixer", layer_spec.part("mixer"))
+        self.mixer_post_norm = build_part("norm", layer_spec.part("mixer_post_norm"))
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if "feed_forward" in layer_spec.parts:
+            self.feed_forward_norm = build_part("norm", layer_spec.part("feed_forward_norm"))
+            self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward"))
+            self.feed_forward_post_norm = build_part("norm", layer_spec.part("feed_forward_post_norm"))
+        for norm in (self.mixer_norm, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward_post_norm):
+            if norm is not None and type(norm).fused_rms is Norm.fused_rms:
+                raise ValueError("sandwich_norm: the norms must be plain RMS norms")
+
+    def sub_parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward,
+                            self.feed_forward_post_norm) if p is not None]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, hidden, delta, ctx, site, writes_cache):
+        weight, eps = self.mixer_norm.fused_rms()
+        if isinstance(delta, PendingNormed):
+            x = torch.empty(hidden.shape, dtype=weight.dtype, device=hidden.device)
+            ops.sandwich_norm(hidden, delta.y, delta.weight, delta.eps, weight, eps, x)
+        else:
+            x = self.mixer_norm.forward(hidden, delta)
+        y = self.mixer.forward(x, ctx, site, writes_cache)
+        post = PendingNormed(y, *self.mixer_post_norm.fused_rms())
+        if self.feed_forward is None:
+            return post
+        weight, eps = self.feed_forward_norm.fused_rms()
+        x = torch.empty(hidden.shape, dtype=weight.dtype, device=hidden.device)
+        ops.sandwich_norm(hidden, post.y, post.weight, post.eps, weight, eps, x)
+        return PendingNormed(self.feed_forward.forward(x, ctx), *self.feed_forward_post_norm.fused_rms())
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich_norm", SandwichBlock)

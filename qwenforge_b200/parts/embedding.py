@@ -36,6 +36,34 @@ class TokenEmbedding(Embedding):
         return hidden
 
 
+class TokenPositionEmbedding(Embedding):
+    """Token embedding plus a learned vector per absolute position, neither scaled: x_t = E[token_t] + P[position_t].
+    params: vocab_size, width, max_positions. tensors: weight [vocab_size, width], positions [max_positions, width]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vocab = int(self.params["vocab_size"])
+        self.width = int(self.params["width"])
+        self.max_positions = int(self.params["max_positions"])
+        self.weight = self.positions = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.file_name("weight"), (self.vocab, self.width)),
+                TensorSpec(self.file_name("positions"), (self.max_positions, self.width))]
+
+    def kernel_libraries(self, dtype):
+        return {"embed"}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.file_name("weight")]
+        self.positions = tensors[self.file_name("positions")]
+
+    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
+        hidden = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
+        ops.embed_positions(token_ids, ctx.tok_pos, self.weight, self.positions, hidden, ctx.err)
+        return hidden
+
+
 class LinearHead(Part):
     """params: vocab_size, width, tied. tensors: weight [vocab_size, width] (the embedding's tensor when tied), and
     optionally weight_fallback: the tensor that serves when the files hold no `weight` (the reference takes the
@@ -65,4 +93,5 @@ class LinearHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
 register_part("head", "linear_head", LinearHead)

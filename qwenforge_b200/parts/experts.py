@@ -1,0 +1,80 @@
+"""A mixture of small SwiGLU experts chosen per token by a router.
+
+  z = R h (float32)                         router logits
+  s = sigmoid(z)  or  softmax(z)            scores (`score`)
+  the `top` experts with the largest s      weights: their scores, divided by their sum with `renormalize`
+  out = sum_e expert_e(w_e * h)             `weight_on` = "input": the weight multiplies what the expert reads
+     or sum_e w_e * expert_e(h)             `weight_on` = "output"
+  expert(v) = D_e (silu(G_e v) * (U_e v)),  no biases
+
+Routing, sorting by expert and the experts' products all stay on the device (`ops.moe_plan`, `ops.expert_linear`: one
+launch per product for all experts, sized by what any routing can need), so the part is graph safe: a decode graph
+replays it with other routings every step.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec
+from .registry import register_part
+
+
+class RoutedExperts(FeedForward):
+    """params: hidden_size, expert_size, experts, top, score ("sigmoid" | "softmax"), renormalize, weight_on ("input" | "output").
+    tensors: router [E, W], and per expert e: gate.<e> [F, W], up.<e> [F, W], down.<e> [W, F]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["expert_size"])
+        self.n_experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.score = str(p.get("score", "sigmoid"))
+        self.renormalize = bool(p.get("renormalize", False))
+        self.weight_on = str(p.get("weight_on", "output"))
+        if self.score not in ("sigmoid", "softmax") or self.weight_on not in ("input", "output"):
+            raise ValueError(f"routed_experts: score {self.score!r} / weight_on {self.weight_on!r} not understood")
+        if not 1 <= self.top <= min(self.n_experts, 16):
+            raise ValueError(f"routed_experts: top {self.top} of {self.n_experts} experts is not supported (1..16)")
+        self.router = self.gate_up = self.down = None
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.file_name("router"), (self.n_experts, self.hidden))]
+        for e in range(self.n_experts):
+            specs += [TensorSpec(self.file_name(f"gate.{e}"), (self.inter, self.hidden)),
+                      TensorSpec(self.file_name(f"up.{e}"), (self.inter, self.hidden)),
+                      TensorSpec(self.file_name(f"down.{e}"), (self.hidden, self.inter))]
+        return specs
+
+    def kernel_libraries(self, dtype):
+        return {"activation", "moe", "grouped_gemm"} | ({"gemm_f32"} if dtype == torch.float32 else set())
+
+    def bind(self, tensors, dtype, device):
+        t = lambda logical: tensors[self.file_name(logical)]
+        self.router = t("router")
+        self.gate_up = torch.stack([torch.cat((t(f"gate.{e}"), t(f"up.{e}")), dim=0) for e in range(self.n_experts)]).contiguous()
+        self.down = torch.stack([t(f"down.{e}") for e in range(self.n_experts)]).contiguous()
+
+    def step_weights(self):
+        return [self.router, self.gate_up, self.down]
+
+    def forward(self, x, ctx):
+        # float32 logits from the rows as the experts see them (their bfloat16 rounding on the 16-bit path: products of
+        # bfloat16 numbers are exact in float32, and the sums are float32)
+        logits = ops.linear(x, self.router, out_dtype=torch.float32)
+        plan = ops.moe_plan(logits, self.top, self.score == "softmax", self.renormalize)
+        rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
+        ops.moe_gather(x, plan, rows, self.weight_on == "input")
+        gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
+        ops.expert_linear(rows, self.gate_up, plan, gate_up)
+        act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
+        ops.swiglu(gate_up, act)
+        ops.expert_linear(act, self.down, plan, rows)
+        out = torch.empty_like(x)
+        ops.moe_combine(rows, plan, out, self.weight_on == "output")
+        return out
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

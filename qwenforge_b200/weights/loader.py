@@ -5,6 +5,7 @@
   keep="compute"  the activation dtype: bfloat16, or float32 on the 32-bit path
   keep="stored"   as the file stores it when that is a 32-bit float, else like "compute"
   keep="int32"    integer tables as int32
+  keep="float32"  float32 in both precisions (a few numbers that enter 32-bit arithmetic, such as attention sinks)
 Anything that does not line up is reported in ONE `WeightsError` that lists every missing
 tensor, every unexpected tensor and every wrong shape. The file layout follows the reference's
 loader (utils/load_weights.py:49-73): `model.safetensors.index.json`'s `weight_map` if present,
@@ -66,6 +67,8 @@ def merge_specs(specs: Iterable[TensorSpec]) -> dict[str, TensorSpec]:
 def kept_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
     if spec.keep == "int32":
         return torch.int32
+    if spec.keep == "float32":
+        return torch.float32
     if spec.keep == "stored" and stored == torch.float32:
         return torch.float32
     return compute
@@ -78,10 +81,12 @@ def _list(items: Sequence[str], limit: int = 12) -> str:
 
 
 def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, device,
-                 redundant: Optional[Mapping[str, str]] = None) -> dict[str, torch.Tensor]:
-    """`redundant`: names the files may hold beyond the wanted ones, each mapped to the wanted tensor it must equal."""
+                 redundant: Optional[Mapping[str, str]] = None, ignored: Sequence[str] = ()) -> dict[str, torch.Tensor]:
+    """`redundant`: names the files may hold beyond the wanted ones, each mapped to the wanted tensor it must equal.
+    `ignored`: names the files may hold that nothing reads."""
     wanted = merge_specs(specs)
     redundant = dict(redundant or {})
+    ignored = set(ignored)
     files = [SafetensorsFile(p) for p in weight_files(model_dir)]
     try:
         where: dict[str, SafetensorsFile] = {}
@@ -93,7 +98,7 @@ def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, dev
                 where[name] = f
         source = {n: (n if n in where or s.fallback not in where else s.fallback) for n, s in wanted.items()}
         missing = sorted(n for n in wanted if source[n] not in where)
-        unexpected = sorted(n for n in where if n not in wanted and n not in redundant)
+        unexpected = sorted(n for n in where if n not in wanted and n not in redundant and n not in ignored)
         wrong_shape, wrong_dtype = [], []
         for extra, twin in redundant.items():
             if extra in where and extra not in wanted and twin in where:

@@ -25,6 +25,8 @@ def draw_tensor(spec: TensorSpec, generator: torch.Generator, store_dtype: torch
         value = 1.0 + 0.1 * noise
     elif spec.init in ("matrix", "bias"):
         value = 0.02 * noise
+    elif spec.init == "logit":
+        value = noise
     else:
         raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
     return value if spec.keep == "stored" else value.to(store_dtype)
@@ -45,14 +47,14 @@ def random_state_on_device(specs, seed: int, dtype: torch.dtype, device) -> dict
         if spec.keep == "int32":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        if spec.init not in ("norm", "matrix", "bias"):
+        if spec.init not in ("norm", "matrix", "bias", "logit"):
             raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
-        kept = torch.float32 if spec.keep == "stored" else dtype
+        kept = torch.float32 if spec.keep in ("stored", "float32") else dtype
         value = torch.empty(spec.shape, dtype=kept, device=device)
         flat = value.view(-1)
         for begin in range(0, flat.numel(), 1 << 27):  # float32 draws of at most 512 MB at a time
             noise = torch.randn(min(1 << 27, flat.numel() - begin), generator=generator, dtype=torch.float32, device=device)
-            noise = 1.0 + 0.1 * noise if spec.init == "norm" else 0.02 * noise
+            noise = 1.0 + 0.1 * noise if spec.init == "norm" else noise if spec.init == "logit" else 0.02 * noise
             flat[begin:begin + noise.numel()] = noise.to(kept)
         out[name] = value
     return out

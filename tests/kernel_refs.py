@@ -111,7 +111,16 @@ def gather_kv(site, slot, lo, hi):
     return _f(k).transpose(0, 1), _f(v).transpose(0, 1)
 
 
-def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, scratch=None, max_kv_len=None):
+def gather_keys(site, slot, lo, hi):
+    """Rows lo..hi-1 of a one-plane cache: [kv_heads, hi-lo, head_dim] float64."""
+    pos = torch.arange(lo, hi, device=site.table.device)
+    pages = site.table[slot, pos // PAGE].long()
+    assert bool((pages >= 0).all()), "reference: read of a page that is not held"
+    return _f(site.storage[pages, 0, :, pos % PAGE, :]).transpose(0, 1)
+
+
+def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, scratch=None, max_kv_len=None,
+                      sinks=None, shared_values=False):
     d, kvh = site.head_dim, site.kv_heads
     groups = n_heads // kvh
     for s in range(n_seqs):
@@ -123,12 +132,19 @@ def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q
         for t in range(b, e):
             p = int(tok_pos[t])
             lo = max(0, p - window + 1) if window > 0 else 0
-            k, v = gather_kv(site, slot, lo, p + 1)
+            if shared_values:
+                k = v = gather_keys(site, slot, lo, p + 1)
+            else:
+                k, v = gather_kv(site, slot, lo, p + 1)
             qt = _f(q[t]).view(n_heads, d)
             k = k.repeat_interleave(groups, dim=0)
             v = v.repeat_interleave(groups, dim=0)
             scores = torch.einsum("hd,hjd->hj", qt, k) * scale
-            ctx = torch.einsum("hj,hjd->hd", torch.softmax(scores, -1), v)
+            if sinks is not None:   # one more term in the denominator, with no value
+                weights = torch.softmax(torch.cat((scores, _f(sinks)[:, None]), dim=-1), -1)[:, :-1]
+            else:
+                weights = torch.softmax(scores, -1)
+            ctx = torch.einsum("hj,hjd->hd", weights, v)
             out[t] = ctx.reshape(-1).to(out.dtype)
 
 
@@ -146,6 +162,93 @@ def sample(logits, temperature, seed, seq_ids, steps, out, scratch=None):
         out[r] = token
 
 
-ALL = dict(embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
+def _rms(x, weight, eps):
+    x = _f(x)
+    return x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * _f(weight)
+
+
+def embed_positions(ids, tok_pos, table, positions, out, err):
+    out.copy_((_f(table[ids.long()]) + _f(positions[tok_pos.long()])).to(torch.float32))
+
+
+def sandwich_norm(hidden, y, post_weight, post_eps, next_weight=None, next_eps=0.0, out=None):
+    hidden += _rms(y, post_weight, post_eps).to(torch.float32)
+    if next_weight is not None:
+        out.copy_(_rms(hidden, next_weight, next_eps).to(out.dtype))
+
+
+def clamped_glu(gate_up, limit, alpha, out):
+    inter = gate_up.shape[1] // 2
+    g = _f(gate_up[:, :inter]).clamp(max=limit)
+    u = _f(gate_up[:, inter:]).clamp(min=-limit, max=limit)
+    out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
+
+
+def latent_norm_cache(down, q_rank, q_norm, kv_norm, eps, tok_seq, tok_pos, slots, q_latent, site, write_cache, err, latent_out=None):
+    if q_rank:
+        q_latent.copy_(_rms(down[:, :q_rank], q_norm, eps).to(q_latent.dtype))
+    c = _rms(down[:, q_rank:], kv_norm, eps)
+    if latent_out is not None:
+        latent_out.copy_(c.to(latent_out.dtype))
+    if not write_cache:
+        return
+    for t in range(down.shape[0]):
+        slot = int(slots[int(tok_seq[t])])
+        if slot < 0:
+            continue
+        pos = int(tok_pos[t])
+        page = int(site.table[slot, pos // PAGE])
+        assert page >= 0, "reference: write to a page that is not held"
+        site.storage[page, 0, 0, pos % PAGE, :] = c[t].to(site.storage.dtype)
+
+
+def head_linear(x, weight, out):
+    groups, n, k = weight.shape
+    y = torch.einsum("tgk,gnk->tgn", _f(x).view(x.shape[0], groups, k), _f(weight))
+    out.copy_(y.reshape(x.shape[0], groups * n).to(out.dtype))
+
+
+class _Routing:
+    pass
+
+
+def moe_plan(logits, top, softmax_scores=False, renormalize=False):
+    z = logits.to(torch.float32)
+    scores = torch.softmax(z, -1) if softmax_scores else torch.sigmoid(z)
+    chosen = torch.topk(scores, top, dim=-1)
+    weights = chosen.values / chosen.values.sum(-1, keepdim=True) if renormalize else chosen.values
+    plan = _Routing()
+    plan.n_tokens, plan.n_experts, plan.top, plan.pairs = z.shape[0], z.shape[1], top, z.shape[0] * top
+    experts = chosen.indices.reshape(-1)
+    order = torch.sort(experts, stable=True).indices                    # rows: pairs sorted by expert
+    plan.sorted_token = (order // top).to(torch.int32)
+    plan.sorted_weight = weights.reshape(-1)[order].to(torch.float32)
+    plan.row_expert = experts[order]
+    plan.dest = torch.empty(plan.pairs, dtype=torch.int32)
+    plan.dest[order] = torch.arange(plan.pairs, dtype=torch.int32)
+    return plan
+
+
+def moe_gather(x, plan, out, scale_input):
+    rows = _f(x)[plan.sorted_token.long()]
+    if scale_input:
+        rows = rows * _f(plan.sorted_weight)[:, None]
+    out.copy_(rows.to(out.dtype))
+
+
+def moe_combine(y, plan, out, scale_output):
+    rows = _f(y)
+    if scale_output:
+        rows = rows * _f(plan.sorted_weight)[:, None]
+    out.copy_(rows[plan.dest.long()].view(plan.n_tokens, plan.top, -1).sum(1).to(out.dtype))
+
+
+def expert_linear(x, weight, plan, out):
+    out.copy_(torch.einsum("rk,rnk->rn", _f(x), _f(weight)[plan.row_expert]).to(out.dtype))
+
+
+ALL = dict(embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
+           head_linear=head_linear, moe_plan=moe_plan, moe_gather=moe_gather, moe_combine=moe_combine, expert_linear=expert_linear,
+           embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
            linear=linear, rope_cache_write=rope_cache_write, attention_generic=attention_generic, swiglu=swiglu,
            sample=sample)

@@ -1,0 +1,425 @@
+"""The Mefepel design on a GPU: each new kernel against its plain reference, the model against the plain implementation
+(tests/plain_mefepel.py) whole, decoded, cut into portions, in unequal batches, in slots and pages used before, and
+through the engine's own entry point with greedy generation. The tests make their own small configurations
+(tests/helpers_mefepel.py) and weights; where random weights would hide a fault, inputs are made so that it shows."""
+import math
+
+import pytest
+import torch
+
+from tests import kernel_refs as refs
+from tests import plain_mefepel as plain
+from tests.helpers import max_err, random_tokens
+from tests.helpers_mefepel import CONFIGS, MEF_FAST, MEF_ODD, MEF_WIDE, config, dense, layer, make_model_dir, mixer, moe
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def close(got, want, dtype, what=""):
+    """float32: rounding of sums only. bfloat16: 8 bits of mantissa in every activation."""
+    got, want = got.double().cpu(), want.double().cpu()
+    scale = float(want.abs().max()) + 1e-9
+    bound = (3e-5 if dtype == torch.float32 else 3e-2) * scale
+    err = float((got - want).abs().max())
+    assert err <= bound, f"{what}: max |diff| {err:.3e} exceeds {bound:.3e}"
+
+
+def logits_close(got, want, dtype, what=""):
+    """Like the design's own measure: the difference with its mean taken off, root mean square over the vocabulary,
+    against the spread of the logits."""
+    got, want = got.double().cpu(), want.double().cpu()
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    err = d.square().mean(-1).sqrt() / want.std(-1)
+    bound = 1e-4 if dtype == torch.float32 else 6e-2
+    assert float(err.max()) <= bound, f"{what}: worst row {float(err.max()):.3e} exceeds {bound:.1e}"
+
+
+# ------------------------------------------------------------------------------------------------ kernels alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_positions(dtype):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    table, pos = torch.randn(50, 37, generator=g).to(dtype).to(DEV), torch.randn(90, 37, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, 50, (23,), generator=g).int().to(DEV)
+    places = torch.randint(0, 90, (23,), generator=g).int().to(DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(23, 37, dtype=torch.float32, device=DEV)
+    ops.embed_positions(ids, places, table, pos, out, err)
+    want = torch.empty_like(out)
+    refs.embed_positions(ids, places, table, pos, want, err)
+    assert max_err(out, want) < 1e-6 and int(err) == 0
+    places[3] = 90
+    ops.embed_positions(ids, places, table, pos, out, err)
+    assert int(err) == ops.ERR_POSITION_RANGE
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [52, 320, 5000])
+def test_sandwich_norm(dtype, width):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(width)
+    hidden = torch.randn(7, width, generator=g).to(DEV)
+    y = (3 * torch.randn(7, width, generator=g)).to(dtype).to(DEV)
+    w1, w2 = (1 + 0.2 * torch.randn(width, generator=g)).to(dtype).to(DEV), (1 + 0.2 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    want_h, want_out = hidden.clone(), torch.empty(7, width, dtype=dtype, device=DEV)
+    refs.sandwich_norm(want_h, y, w1, 1e-5, w2, 2e-5, want_out)
+    out = torch.empty_like(want_out)
+    ops.sandwich_norm(hidden, y, w1, 1e-5, w2, 2e-5, out)
+    assert max_err(hidden, want_h) < 2e-5
+    close(out, want_out, dtype, "normed stream")
+    only_add = want_h.clone()
+    refs.sandwich_norm(only_add, y, w1, 1e-5)
+    ops.sandwich_norm(hidden, y, w1, 1e-5)
+    assert max_err(hidden, only_add) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_clamped_glu_clamps_both_halves(dtype):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    gate_up = (4 * torch.randn(9, 2 * 45, generator=g)).to(dtype).to(DEV)   # many values beyond the limit on both sides
+    out, want = torch.empty(9, 45, dtype=dtype, device=DEV), torch.empty(9, 45, dtype=dtype, device=DEV)
+    ops.clamped_glu(gate_up, 1.25, 1.702, out)
+    refs.clamped_glu(gate_up, 1.25, 1.702, want)
+    close(out, want, dtype)
+    gate = gate_up[:, :45].float()
+    assert bool((gate > 1.25).any()) and bool((gate < -1.25).any())   # the gate is clamped from above only
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 10, 36, 5), (4, 16, 64, 70), (20, 8, 128, 200), (2, 24, 50, 33)])
+def test_head_linear(dtype, shape):
+    from qwenforge_b200 import ops
+    heads, k, n, rows = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(rows, heads * k, generator=g).to(dtype).to(DEV)
+    w = torch.randn(heads, n, k, generator=g).to(dtype).to(DEV)
+    out, want = torch.empty(rows, heads * n, dtype=dtype, device=DEV), torch.empty(rows, heads * n, dtype=dtype, device=DEV)
+    ops.head_linear(x, w, out)
+    refs.head_linear(x, w, want)
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(37, 5, 2, 52, 22), (300, 6, 3, 128, 64), (1, 4, 1, 96, 40), (130, 3, 3, 40, 24)])
+def test_routing_and_expert_products(dtype, shape):
+    """Routing, sorting by expert, the gathered rows, both grouped products and the combination, against the references;
+    with an expert that nobody chooses and one that nearly everybody does."""
+    from qwenforge_b200 import ops
+    tokens, experts, top, width, ff = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    logits = torch.randn(tokens, experts, generator=g)
+    logits[:, 0] -= 30.0          # never among the chosen (unless top == experts)
+    logits[:, 1] += 3.0           # nearly always
+    logits = logits.to(DEV)
+    x = torch.randn(tokens, width, generator=g).to(dtype).to(DEV)
+    w1 = (torch.randn(experts, 2 * ff, width, generator=g) / math.sqrt(width)).to(dtype).to(DEV)
+    w2 = (torch.randn(experts, width, ff, generator=g) / math.sqrt(ff)).to(dtype).to(DEV)
+    plan, want_plan = ops.moe_plan(logits, top), refs.moe_plan(logits.cpu(), top)
+    offsets = plan.offsets.cpu().tolist()
+    counts = torch.bincount(want_plan.row_expert, minlength=experts).tolist()
+    assert [offsets[e + 1] - offsets[e] for e in range(experts)] == counts
+    dest, sorted_token, sorted_weight = plan.dest.cpu().long(), plan.sorted_token.cpu().long(), plan.sorted_weight.cpu()
+    scores = torch.sigmoid(logits.cpu())
+    chosen = torch.topk(scores, top).indices
+    for t in range(tokens):
+        for j in range(top):
+            row = int(dest[t * top + j])
+            e = int(chosen[t, j])
+            assert offsets[e] <= row < offsets[e + 1] and int(sorted_token[row]) == t
+            assert abs(float(sorted_weight[row]) - float(scores[t, e])) < 1e-6
+    n_tiles = int(plan.n_tiles)
+    assert n_tiles == sum(-(-c // ops.kernels.GROUP_TILE_ROWS) for c in counts) <= plan.max_tiles
+    # the whole feed-forward, with the weight on the input
+    rows = torch.empty(plan.pairs, width, dtype=dtype, device=DEV)
+    ops.moe_gather(x, plan, rows, True)
+    want_rows = (x.double()[sorted_token.to(DEV)] * sorted_weight.to(DEV).double()[:, None])
+    close(rows, want_rows, dtype, "gathered rows")
+    gate_up = torch.empty(plan.pairs, 2 * ff, dtype=dtype, device=DEV)
+    ops.expert_linear(rows, w1, plan, gate_up)
+    row_expert = torch.empty(plan.pairs, dtype=torch.long)
+    for e in range(experts):
+        row_expert[offsets[e]:offsets[e + 1]] = e
+    want_gu = torch.einsum("rk,rnk->rn", rows.double(), w1.double()[row_expert.to(DEV)])
+    close(gate_up, want_gu, dtype, "gate/up of the experts")
+    act = torch.empty(plan.pairs, ff, dtype=dtype, device=DEV)
+    ops.swiglu(gate_up, act)
+    y = torch.empty(plan.pairs, width, dtype=dtype, device=DEV)
+    ops.expert_linear(act, w2, plan, y)
+    close(y, torch.einsum("rk,rnk->rn", act.double(), w2.double()[row_expert.to(DEV)]), dtype, "down of the experts")
+    out = torch.empty(tokens, width, dtype=dtype, device=DEV)
+    ops.moe_combine(y, plan, out, False)
+    close(out, y.double()[dest.to(DEV)].view(tokens, top, width).sum(1), dtype, "combined")
+
+
+def _latent_case(dtype, rank, heads, lengths, new, seed, sink_value=None):
+    """A one-plane cache filled with random latents for sequences of `lengths`, queries for their last `new` positions."""
+    from qwenforge_b200 import ops
+    from qwenforge_b200.cache import KvNeed, SequenceCache
+    g = torch.Generator().manual_seed(seed)
+    cache = SequenceCache([KvNeed(1, rank, 0, planes=1)], 64 * 40, 8, 2048, dtype, DEV)
+    slots = [cache.open() for _ in lengths]
+    cache.reserve(list(zip(slots, lengths)))
+    cache.flush()
+    site = cache.site(0)
+    latents = []
+    for slot, n in zip(slots, lengths):
+        c = torch.randn(n, rank, generator=g).to(dtype)
+        latents.append(c)
+        pages = site.table[slot, torch.arange(n, device=DEV) // 64].long()
+        site.storage[pages, 0, 0, torch.arange(n, device=DEV) % 64] = c.to(DEV)
+    q = torch.randn(sum(new), heads * rank, generator=g).to(dtype).to(DEV)
+    sinks = (torch.randn(heads, generator=g) * 2 if sink_value is None else torch.full((heads,), sink_value)).float().to(DEV)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    tok_pos = torch.cat([torch.arange(L - n, L) for L, n in zip(lengths, new)]).int().to(DEV)
+    ctx = dict(cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), tok_pos=tok_pos, slots=torch.tensor(slots, dtype=torch.int32, device=DEV))
+    return cache, site, ops.KvSiteArgs(site.storage, site.table, 1, rank), latents, q, sinks, ctx
+
+
+def _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale):
+    rows, o = [], 0
+    for c, L, n in zip(latents, lengths, new):
+        c = c.double()
+        for i in range(n):
+            p = L - n + i
+            qt = q[o + i].double().cpu().view(heads, rank)
+            s = scale * qt @ c[:p + 1].T
+            w = plain.sink_softmax(s, sinks.double().cpu()[:, None])
+            rows.append((w @ c[:p + 1]).reshape(-1))
+        o += n
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rank,heads", [(36, 3), (64, 4), (128, 20), (300, 2)])
+def test_generic_attention_with_sinks_over_a_shared_plane(dtype, rank, heads):
+    from qwenforge_b200 import ops
+    lengths, new = [130, 64, 7], [130, 3, 7]
+    cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 5)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    scale = 0.7 / math.sqrt(rank)
+    ops.attention_generic(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 3, max(new), scale, 0, err,
+                          sinks=sinks, shared_values=True)
+    close(out, _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale), dtype)
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("rank,heads", [(32, 5), (64, 4), (96, 3), (128, 20)])
+def test_tensor_core_attention_with_sinks_over_a_shared_plane(rank, heads):
+    """The mma.sync prefill kernel and the split-K decode kernel read the latent plane as keys and as values and count the
+    sink once, also when a sequence's runs are folded by the block with the last ticket."""
+    from qwenforge_b200 import ops
+    dtype = torch.bfloat16
+    scale = 0.7 / math.sqrt(rank)
+    lengths, new = [700, 65, 129], [200, 65, 2]
+    cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 6)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    ops.attention_prefill(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 3, max(new), scale, 0, err,
+                          max_kv_len=max(lengths), sinks=sinks, shared_values=True)
+    close(out, _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale), dtype, "prefill")
+    for n_splits in (1, 4):
+        lengths, new = [1500, 64, 65, 1], [1, 1, 1, 1]
+        cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 7 + n_splits)
+        scratch = ops.DecodeScratch(torch.device(DEV))
+        out = torch.empty_like(q)
+        ops.attention_decode(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 4, scale, 0, n_splits, scratch, err,
+                             sinks=sinks, shared_values=True)
+        close(out, _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale), dtype, f"decode, {n_splits} splits")
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("kernel", ["generic", "prefill", "decode"])
+def test_a_large_sink_takes_the_weight_and_a_small_one_none(kernel):
+    """With a sink far above every score the output vanishes; far below, the result is the plain softmax's."""
+    from qwenforge_b200 import ops
+    dtype, rank, heads, scale = torch.bfloat16, 64, 4, 0.1
+    lengths, new = ([300], [1]) if kernel == "decode" else ([300], [100])
+    for sink_value, what in ((60.0, "large"), (-60.0, "small")):
+        cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 9, sink_value)
+        err = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.empty_like(q)
+        if kernel == "generic":
+            ops.attention_generic(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, max(new), scale, 0, err,
+                                  sinks=sinks, shared_values=True)
+        elif kernel == "prefill":
+            ops.attention_prefill(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, max(new), scale, 0, err,
+                                  sinks=sinks, shared_values=True)
+        else:
+            ops.attention_decode(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, scale, 0, 2,
+                                 ops.DecodeScratch(torch.device(DEV)), err, sinks=sinks, shared_values=True)
+        want = _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale)
+        close(out, want, dtype, f"{kernel}, {what} sink")
+        assert (float(want.abs().max()) < 1e-6) == (what == "large")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_norm_cache_writes_each_token_to_its_own_place(dtype):
+    from qwenforge_b200 import ops
+    from qwenforge_b200.cache import KvNeed, SequenceCache
+    q_rank, rank = 20, 36
+    cache = SequenceCache([KvNeed(1, rank, 0, planes=1)], 64 * 8, 4, 512, dtype, DEV)
+    a, b = cache.open(), cache.open()
+    cache.reserve([(a, 70), (b, 3)])
+    cache.flush()
+    site = cache.site(0)
+    args = ops.KvSiteArgs(site.storage, site.table, 1, rank)
+    g = torch.Generator().manual_seed(3)
+    down = torch.randn(9, q_rank + rank, generator=g).to(DEV)
+    wq, wkv = (1 + 0.2 * torch.randn(q_rank, generator=g)).to(dtype).to(DEV), (1 + 0.2 * torch.randn(rank, generator=g)).to(dtype).to(DEV)
+    tok_seq = torch.tensor([0] * 6 + [1] * 3, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([62, 63, 64, 65, 66, 67, 0, 1, 2], dtype=torch.int32, device=DEV)   # across a page border
+    slots = torch.tensor([a, b], dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_latent = torch.empty(9, q_rank, dtype=dtype, device=DEV)
+    plain_out = torch.empty(9, rank, dtype=dtype, device=DEV)
+    ops.latent_norm_cache(down, q_rank, wq, wkv, 1e-5, tok_seq, tok_pos, slots, q_latent, args, True, err, latent_out=plain_out)
+    close(q_latent, refs._rms(down[:, :q_rank], wq, 1e-5), dtype, "query latent")
+    want = refs._rms(down[:, q_rank:], wkv, 1e-5)
+    close(plain_out, want, dtype, "latent")
+    for t in range(9):
+        slot, pos = int(slots[int(tok_seq[t])]), int(tok_pos[t])
+        page = int(site.table[slot, pos // 64])
+        assert torch.equal(site.storage[page, 0, 0, pos % 64], plain_out[t])
+    assert int(err) == 0
+
+
+# ------------------------------------------------------------------------------------------------ the model
+def build(cfg, tmp_path, dtype, seed=0, spread=1.0):
+    from qwenforge_b200.engine import Model
+    folder, weights = make_model_dir(cfg, seed, tmp_path, spread=spread)
+    return Model.from_dir(folder, dtype, DEV), weights, folder
+
+
+def run_cuts(model, cache, tokens, cuts, want_all=True):
+    """Feed `tokens` in steps of the given sizes through one slot; returns the logits of every position."""
+    slot = cache.open()
+    rows, at = [], 0
+    for n in cuts:
+        rows.append(model.step(cache, [(slot, tokens[at:at + n])], want=[list(range(n))]))
+        at += n
+    assert at == len(tokens)
+    cache.close(slot)
+    model.raise_on_kernel_error()
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompts_decoding_and_portions(name, dtype, tmp_path):
+    cfg = CONFIGS[name]
+    model, weights, _ = build(cfg, tmp_path, dtype)
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    cache = model.new_cache(64 * 12, 4)
+    tokens = random_tokens(cfg["vocab"], 200, 4)
+    want = plain.forward_logits(cfg, weights, tokens)
+    for cuts in ([200], [150] + [1] * 50, [64, 64, 64, 8], [63, 2, 65, 2, 2, 66], [1] * 3 + [197], [2] * 100):
+        got = run_cuts(model, cache, tokens, cuts)
+        logits_close(got, want, torch_dtype, f"{name} cut {cuts[:4]}")
+    # the first tokens of a sequence, alone
+    logits_close(run_cuts(model, cache, tokens[:1], [1]), want[:1], torch_dtype, "one token")
+    assert all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuts_agree_with_one_another_to_rounding(dtype, tmp_path):
+    """float32: what a position's logits are must not depend on the cut beyond the rounding of sums."""
+    cfg = MEF_FAST
+    model, weights, _ = build(cfg, tmp_path, dtype, seed=8)
+    cache = model.new_cache(64 * 12, 4)
+    tokens = random_tokens(cfg["vocab"], 150, 6)
+    whole = run_cuts(model, cache, tokens, [150])
+    for cuts in ([100] + [1] * 50, [7, 64, 79], [2] * 75):
+        got = run_cuts(model, cache, tokens, cuts)
+        logits_close(got, whole, torch.float32 if dtype == "float32" else torch.bfloat16, str(cuts[:3]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["odd", "fast"])
+def test_unequal_batches_against_each_alone_in_reused_slots(name, dtype, tmp_path):
+    cfg = CONFIGS[name]
+    model, weights, _ = build(cfg, tmp_path, dtype, seed=1)
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    cache = model.new_cache(64 * 10, 3)       # three slots for five requests: slots and pages come back
+    seqs = [random_tokens(cfg["vocab"], n, 20 + n) for n in (1, 130, 65, 64, 3)]
+    refs_ = [plain.forward_logits(cfg, weights, s) for s in seqs]
+    tail = 6
+    for round_ in range(2):
+        for batch in ([0, 1, 2], [3, 4]):
+            slots = {i: cache.open() for i in batch}
+            heads = {i: max(1, len(seqs[i]) - tail) for i in batch}
+            logits = model.step(cache, [(slots[i], seqs[i][:heads[i]]) for i in batch], want=[list(range(heads[i])) for i in batch])
+            got, o = {i: [] for i in batch}, 0
+            for i in batch:
+                got[i].append(logits[o:o + heads[i]])
+                o += heads[i]
+            fed = dict(heads)
+            live = [i for i in batch if fed[i] < len(seqs[i])]
+            while live:
+                logits = model.step(cache, [(slots[i], [seqs[i][fed[i]]]) for i in live])
+                for row, i in enumerate(live):
+                    got[i].append(logits[row:row + 1])
+                    fed[i] += 1
+                for i in [i for i in live if fed[i] == len(seqs[i])]:
+                    cache.close(slots.pop(i))       # ends earlier than the others: its slot is free for the next batch
+                live = [i for i in live if fed[i] < len(seqs[i])]
+            for i in list(slots):
+                cache.close(slots.pop(i))
+            for i in batch:
+                logits_close(torch.cat(got[i]), refs_[i], torch_dtype, f"{name} round {round_} request {i}")
+    model.raise_on_kernel_error()
+    assert cache.slots.n_free == cache.max_seqs
+
+
+def _far_key_model(kind):
+    """One layer whose attention is made to hang on ONE far position: queries and keys are scaled up, so that a key that is
+    lost, shifted by one or read from the wrong page changes the logits by far more than rounding."""
+    return config(200, 64, 1500, 1e-5, [layer(mixer(2, 16, 16, 64 if kind == "fast" else 40, 24, 1.0), dense(96, 3.0))])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["fast", "generic"])
+def test_far_keys_and_page_borders_show_in_the_logits(kind, dtype, tmp_path):
+    cfg = _far_key_model(kind)
+    model, weights, folder = build(cfg, tmp_path, dtype, seed=12, spread=3.0)    # wide matrices: a peaked attention
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    tokens = random_tokens(cfg["vocab"], 1100, 9)
+    want = plain.forward_logits(cfg, weights, tokens)
+    # the attention is peaked: dropping the most-attended far key would move the logits
+    cache = model.new_cache(64 * 20, 2)
+    places = [0, 1, 62, 63, 64, 65, 127, 128, 129, 511, 512, 1023, 1024, 1025, 1099]
+    for cuts in ([1100], [1024, 76], [1000] + [1] * 100, [63, 1, 1, 1035]):
+        got = run_cuts(model, cache, tokens, cuts)
+        logits_close(got[places], want[places], torch_dtype, f"{kind} {cuts[:3]}")
+        logits_close(got[-40:], want[-40:], torch_dtype, f"{kind} {cuts[:3]} tail")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_graphs_and_the_entry_point(dtype, tmp_path):
+    """Greedy generation through StudentEngine (its scheduler, decode graphs, sampler) against greedy decoding with the
+    plain implementation: float32 token by token; bfloat16 wherever the plain logits' margin allows a difference."""
+    from qwenforge_b200.engine import StudentEngine
+    cfg = MEF_FAST
+    folder, weights = make_model_dir(cfg, 21, tmp_path)
+    engine = StudentEngine(str(folder), device=DEV, dtype=dtype)
+    assert engine.cuda_graphs      # every part of the design is graph safe
+    prompts = [random_tokens(cfg["vocab"], n, 30 + n) for n in (5, 70, 33)]
+    n_new = 40
+    got = engine.generate_ids(prompts, max_new_tokens=n_new, batch_size=3, ignore_eos=True)
+    for prompt, tokens in zip(prompts, got):
+        assert len(tokens) == n_new
+        seq = list(prompt)
+        for step, token in enumerate(tokens):
+            row = plain.forward_logits(cfg, weights, seq)[-1]
+            best = torch.topk(row, 2)
+            if dtype == "float32" or float(best.values[0] - best.values[1]) > 0.15 * float(row.std()):
+                assert token == int(best.indices[0]), (dtype, step)
+            seq.append(token)   # follow the engine's own choice
+    # a second call runs in the slots and pages of the first
+    again = engine.generate_ids(prompts, max_new_tokens=n_new, batch_size=2, ignore_eos=True)
+    assert again == got
