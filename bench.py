@@ -41,6 +41,9 @@ def parse():
     p.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                    help="run only this named workload (3B: 16 unequal prompts then 256 steps; 7B: batch 64 to context "
                         "8192 at temperature 0.7) and print its line")
+    p.add_argument("--design", default=None, choices=["mefepel"],
+                   help="measure another design's prefill and decode beside the Qwen2 model of equal size (kernel by "
+                        "kernel), instead of the default workload")
     p.add_argument("--no-workloads", action="store_true", help="leave the 3B and 7B workloads out of the default run's points")
     return p.parse_args()
 
@@ -349,6 +352,107 @@ class _StubTokenizer:
         return [" ".join(str(t) for t in row) for row in rows]
 
 
+# Another design beside the Qwen2 model of the same layer sizes: (its preset, the Qwen2 preset, layers to run of both).
+DESIGN_PAIRS = {"mefepel": [("mefepel-0.5b", "qwen2.5-0.5b", None), ("mefepel-3b", "qwen2.5-3b", None)]}
+# what a kernel's label (ops/timing.py) counts as, so that like is laid beside like
+KERNEL_KINDS = (("attention_prefill", "attention (prompt)"), ("attention_decode", "attention (decode)"),
+                ("attention_generic", "attention (plain)"), ("head_linear", "per-head products"),
+                ("expert_linear", "expert products"), ("moe_", "routing"), ("linear", "library products"),
+                ("tc_gemm", "own tcgen05 product"), ("skinny_gemm", "skinny products"), ("wide_gemm", "wide products"),
+                ("fold_project", "fold + output projection"), ("norm", "norms"), ("residual_add", "norms"),
+                ("rope_cache_write", "rotation + cache write"), ("latent_norm_cache", "latent norms + cache write"),
+                ("swiglu", "gates"), ("clamped_glu", "gates"), ("embed", "embedding"), ("gather_rows", "gather + final norm"))
+
+
+def kind_of(label):
+    for prefix, kind in KERNEL_KINDS:
+        if label.startswith(prefix):
+            return kind
+    return label
+
+
+def design_point(preset, layers, args, pk, torch):
+    """Prompt and decode rates of one preset with weights drawn on the device, and the device time of every kind of
+    kernel in one prompt step and one decode step issued launch by launch."""
+    from qwenforge_b200.config import preset_config
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.ops.timing import KernelTimer
+    config = preset_config(preset)
+    spec = config.model_spec()
+    model = Model.from_random(config, seed=3, dtype="bfloat16")
+    n_layers = len(spec.schedule)
+    vocab, batch, context, tokens = spec.vocab_size, args.batch, min(args.context, spec.max_positions), args.prefill_tokens
+    cache = model.new_cache(batch * (context + 64) + tokens + 128, batch + 2)
+    g = torch.Generator().manual_seed(99)
+    prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+    def prompt_step():
+        slot = cache.open()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        model.step(cache, [(slot, prompt)])
+        end.record()
+        torch.cuda.synchronize()
+        cache.close(slot)
+        return start.elapsed_time(end)
+
+    eager = min(prompt_step() for _ in range(4))
+    with KernelTimer() as timer:
+        prompt_step()
+    prompt_kinds = {}
+    for label, calls, ms in timer.totals():
+        prompt_kinds[kind_of(label)] = round(prompt_kinds.get(kind_of(label), 0.0) + ms * 1e3, 1)
+    model.enable_prefill_graphs()
+    replayed = min(prompt_step() for _ in range(5)) if model.prefill_graphs is not None else None
+    model.enable_prefill_graphs(False)
+    ms_step, kernels = timed_decode(model, cache, batch, context, args.steps, max(args.warmup, 3), vocab, torch)
+    # one decode step launch by launch, kernel by kernel, at the same context
+    slots = [cache.open() for _ in range(batch)]
+    for begin in range(0, batch, 8):
+        chunk = slots[begin:begin + 8]
+        model.step(cache, [(s, torch.randint(0, vocab, (context - 4,), generator=g).tolist()) for s in chunk])
+    for _ in range(2):
+        model.step(cache, [(s, [1]) for s in slots])
+    with KernelTimer() as timer:
+        model.step(cache, [(s, [1]) for s in slots])
+    decode_kinds = {}
+    for label, calls, ms in timer.totals():
+        decode_kinds[kind_of(label)] = round(decode_kinds.get(kind_of(label), 0.0) + ms * 1e3, 1)
+    for s in slots:
+        cache.close(s)
+    model.raise_on_kernel_error()
+    weight_bytes = model.step_weight_bytes()
+    read = weight_bytes + cache.read_bytes([context] * batch)
+    best = replayed if replayed is not None else eager
+    out = {"preset": preset, "layers": n_layers, "step_weight_bytes": weight_bytes,
+           "prefill_tokens": tokens, "prefill_ms_eager": round(eager, 3), "prefill_ms_replayed": None if replayed is None else round(replayed, 3),
+           "prefill_tokens_per_s": round(tokens / best * 1e3), "decode_batch": batch, "decode_context": context,
+           "decode_ms_per_step": round(ms_step, 4), "decode_tokens_per_s": round(batch / ms_step * 1e3, 1), "kernels_per_decode_step": kernels,
+           "decode_bytes_per_step": read, "decode_hbm_frac": round(read / (ms_step * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),
+           "cache_bytes_per_token": cache.read_bytes([1]),
+           "prompt_step_us_by_kind": prompt_kinds, "decode_step_us_by_kind": decode_kinds}
+    del model, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_design(args, pk, torch):
+    points = []
+    with torch.inference_mode():
+        for ours, theirs, layers in DESIGN_PAIRS[args.design]:
+            points.append({"design": design_point(ours, layers, args, pk, torch), "beside": design_point(theirs, layers, args, pk, torch)})
+    first = points[0]["design"]
+    line = {"metric": f"decode tokens/s ({args.design}, {first['preset']}, batch {first['decode_batch']}, context {first['decode_context']})",
+            "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, weights drawn on the device)",
+            "config": {"model": first["preset"], "global_batch": first["decode_batch"], "seq_len": first["decode_context"],
+                       "parallelism": "single GPU", "l2": "a step's operands exceed the L2"},
+            "gpu_launches": first["kernels_per_decode_step"] * args.steps, "peaks": pk, "points": points}
+    print(json.dumps(line))
+    return 0
+
+
 def reference_arm(args):
     """The unmodified reference (a plain copy of its tree under baseline/_ref) through its own entry point,
     `StudentEngine(...).generate(prompts, max_new_tokens, batch_size)`, on the same random-weight model folder, batch,
@@ -443,6 +547,8 @@ def main():
     from qwenforge_b200.weights import write_random_model
 
     pk = peaks()
+    if args.design:
+        return run_design(args, pk, torch)
     if args.workload:
         with torch.inference_mode():
             out = run_workload(args.workload, pk, torch, args.layers)

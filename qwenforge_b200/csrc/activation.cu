@@ -74,3 +74,29 @@ QF_EXPORT int qf_clamped_glu(int is_bf16, const void* gu, void* out, int rows, i
         return (int)launch_pdl(clamped_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, inter, total, limit, alpha);
     return (int)launch_pdl(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total, limit, alpha);
 }
+
+// SwiGLU on rows whose input was to be scaled: out[r][i] = silu(s_r * g) * (s_r * u) for the fused [gate | up] product of
+// the UNSCALED rows (W (s h) = s (W h): the scale moves from the product's input to its float32 result).
+template <typename T>
+__global__ void scaled_swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ row_scale, T* __restrict__ out, int inter,
+                                     size_t total) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter, c = i % inter;
+        const float s = row_scale[t];
+        const float g = s * Num<T>::to_f(gu[t * 2 * inter + c]);
+        const float u = s * Num<T>::to_f(gu[t * 2 * inter + inter + c]);
+        out[i] = Num<T>::from_f(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+QF_EXPORT int qf_scaled_swiglu(int is_bf16, const void* gu, const float* row_scale, void* out, int rows, int inter,
+                               cudaStream_t stream) {
+    const size_t total = (size_t)rows * inter;
+    if (total == 0) return 0;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    if (is_bf16)
+        return (int)launch_pdl(scaled_swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, row_scale, (bf16*)out, inter, total);
+    return (int)launch_pdl(scaled_swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, row_scale, (float*)out, inter, total);
+}

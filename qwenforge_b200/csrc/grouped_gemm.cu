@@ -4,12 +4,14 @@
 //   uniform  every group takes all `rows` rows and its own slice of columns: A_g = A[:, g * a_group_cols : + K],
 //            C_g = C[:, g * c_group_cols : + N]. This is a product per attention head (a latent attention's queries
 //            taken into the latent space, its latent outputs taken back to value heads).
-//   ragged   the rows are sorted by group and cut into tiles of QF_GROUP_BM rows by a plan on the device (csrc/moe.cu):
-//            tile i belongs to group tile_group[i], starts at row tile_row0[i] and ends where the group's rows end
-//            (offsets[group + 1]). The grid has a block row for every tile that any routing can have; those beyond
-//            n_tiles[0] end at once. This is the experts of a mixture-of-experts feed-forward.
+//   ragged   the rows are sorted by group and cut into tiles of `tile_rows` rows (64 or 128) by a plan on the device
+//            (csrc/moe.cu): tile i belongs to group tile_group[i], starts at row tile_row0[i] and ends where the group's
+//            rows end (offsets[group + 1]). The grid has a block row for every tile that any routing can have; those
+//            beyond n_tiles[0] end at once. This is the experts of a mixture-of-experts feed-forward. With `a_rows`,
+//            row r of A is read from A[a_rows[r]]: the sorted rows are gathered on the way in and never stored.
 // W_g = W + g * w_group_stride, row-major [N][K] with leading dimension ldw.
 //
+// Tiles are 64 x 64 (four warps) or, where there are rows enough, 128 x 128 (eight warps, three stages of K in flight).
 // bfloat16 runs on the tensor cores (mma.sync m16n8k16, float32 accumulators, cp.async double buffering) when K and all
 // strides are multiples of 8 elements and the bases 16-byte aligned; anything else, and float32, runs a plain tiled
 // kernel in which every output element is one chain of fused multiply-adds over k = 0 .. K-1 (no TF32). In both, a
@@ -29,9 +31,11 @@ struct GroupedArgs {
     const int* offsets;
     const int* n_tiles;
     int max_tiles;
+    const int* a_rows;       // null: row r of A is row r
 };
 
 // Which group and which rows this block has; false if it has none.
+template <int BM>
 __device__ __forceinline__ bool grouped_tile(const GroupedArgs& g, int& group, int& row0, int& row_end) {
     if (g.tile_group) {
         if ((int)blockIdx.y >= g.n_tiles[0]) return false;
@@ -40,7 +44,7 @@ __device__ __forceinline__ bool grouped_tile(const GroupedArgs& g, int& group, i
         row_end = min(g.offsets[group + 1], g.rows);
     } else {
         group = blockIdx.z;
-        row0 = blockIdx.y * QF_GROUP_BM;
+        row0 = blockIdx.y * BM;
         row_end = g.rows;
     }
     return row0 < row_end;
@@ -56,7 +60,7 @@ grouped_gemm_plain_kernel(GroupedArgs g) {
     __shared__ float a_s[GG_BK][QF_GROUP_BM + 1];
     __shared__ float w_s[GG_BK][GG_BN + 1];
     int group, m0, m_end;
-    if (!grouped_tile(g, group, m0, m_end)) return;
+    if (!grouped_tile<QF_GROUP_BM>(g, group, m0, m_end)) return;
     const T* A = (const T*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
     const T* W = (const T*)g.w + (long long)group * g.w_group_stride;
     T* C = (T*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
@@ -74,7 +78,7 @@ grouped_gemm_plain_kernel(GroupedArgs g) {
             const int idx = threadIdx.x + i * 256;
             const int r = idx / GG_BK, k = idx % GG_BK;
             const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
-            a_s[k][r] = (gm < m_end && gk < K) ? Num<T>::to_f(A[(long long)gm * g.lda + gk]) : 0.f;
+            a_s[k][r] = (gm < m_end && gk < K) ? Num<T>::to_f(A[(long long)(g.a_rows ? g.a_rows[gm] : gm) * g.lda + gk]) : 0.f;
             w_s[k][r] = (gn < N && gk < K) ? Num<T>::to_f(W[(long long)gn * g.ldw + gk]) : 0.f;
         }
         __syncthreads();
@@ -114,12 +118,18 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
     __shared__ __align__(16) bf16 a_s[2][QF_GROUP_BM][GT_LD];
     __shared__ __align__(16) bf16 w_s[2][GG_BN][GT_LD];
     int group, m0, m_end;
-    if (!grouped_tile(g, group, m0, m_end)) return;
+    if (!grouped_tile<QF_GROUP_BM>(g, group, m0, m_end)) return;
     const bf16* A = (const bf16*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
     const bf16* W = (const bf16*)g.w + (long long)group * g.w_group_stride;
     bf16* C = (bf16*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
     const int n0 = blockIdx.x * GG_BN, N = g.n, K = g.k;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wy = warp >> 1, wx = warp & 1;
+    long long a_row[2];   // the two rows of A this thread fetches, through the row map if there is one
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int gm = m0 + ((threadIdx.x + i * 128) >> 2);
+        a_row[i] = gm < m_end ? (g.a_rows ? g.a_rows[gm] : gm) : -1;
+    }
 
     auto fetch = [&](int k0, int buf) {
         // 64 rows x 4 chunks of 8 columns for each operand; 128 threads take two chunks of each
@@ -128,8 +138,8 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
             const int idx = threadIdx.x + i * 128;
             const int r = idx >> 2, c = (idx & 3) * 8;
             const bool k_ok = k0 + c < K;
-            const bool a_ok = k_ok && m0 + r < m_end, w_ok = k_ok && n0 + r < N;
-            cp_async_16(&a_s[buf][r][c], a_ok ? A + (long long)(m0 + r) * g.lda + k0 + c : A, a_ok);
+            const bool a_ok = k_ok && a_row[i] >= 0, w_ok = k_ok && n0 + r < N;
+            cp_async_16(&a_s[buf][r][c], a_ok ? A + a_row[i] * g.lda + k0 + c : A, a_ok);
             cp_async_16(&w_s[buf][r][c], w_ok ? W + (long long)(n0 + r) * g.ldw + k0 + c : W, w_ok);
         }
     };
@@ -185,23 +195,136 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
         }
 }
 
+// The large tile: 128 x 128, eight warps as 2 x 4, warp (wy, wx) a quarter of 64 x 32 as 4 x 4 tiles of m16n8k16; slabs of
+// 32 columns of K, three in flight.
+#define GL_BM 128
+#define GL_BN 128
+#define GL_STAGES 3
+__global__ void __launch_bounds__(256)
+grouped_gemm_mma_large_kernel(GroupedArgs g) {
+    grid_chain_entry();
+    extern __shared__ __align__(16) unsigned char gl_smem[];
+    bf16 (*a_s)[GL_BM][GT_LD] = reinterpret_cast<bf16 (*)[GL_BM][GT_LD]>(gl_smem);
+    bf16 (*w_s)[GL_BN][GT_LD] = reinterpret_cast<bf16 (*)[GL_BN][GT_LD]>(gl_smem + (size_t)GL_STAGES * GL_BM * GT_LD * sizeof(bf16));
+    int group, m0, m_end;
+    if (!grouped_tile<GL_BM>(g, group, m0, m_end)) return;
+    const bf16* A = (const bf16*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
+    const bf16* W = (const bf16*)g.w + (long long)group * g.w_group_stride;
+    bf16* C = (bf16*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
+    const int n0 = blockIdx.x * GL_BN, N = g.n, K = g.k;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wy = warp >> 2, wx = warp & 3;
+    long long a_row[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int gm = m0 + ((threadIdx.x + i * 256) >> 2);
+        a_row[i] = gm < m_end ? (g.a_rows ? g.a_rows[gm] : gm) : -1;
+    }
+    auto fetch = [&](int k0, int buf) {
+        // 128 rows x 4 chunks of 8 columns for each operand; 256 threads take two chunks of each
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 2, c = (idx & 3) * 8;
+            const bool k_ok = k0 + c < K;
+            const bool a_ok = k_ok && a_row[i] >= 0, w_ok = k_ok && n0 + r < N;
+            cp_async_16(&a_s[buf][r][c], a_ok ? A + a_row[i] * g.lda + k0 + c : A, a_ok);
+            cp_async_16(&w_s[buf][r][c], w_ok ? W + (long long)(n0 + r) * g.ldw + k0 + c : W, w_ok);
+        }
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    const int n_slabs = (K + GT_BK - 1) / GT_BK;
+    for (int s = 0; s < GL_STAGES - 1; ++s) {
+        if (s < n_slabs) fetch(s * GT_BK, s);
+        cp_async_commit();
+    }
+    for (int slab = 0; slab < n_slabs; ++slab) {
+        cp_async_wait<GL_STAGES - 2>();
+        __syncthreads();   // slab `slab` has arrived for everyone, and everyone is done with the buffer fetched next
+        if (slab + GL_STAGES - 1 < n_slabs) fetch((slab + GL_STAGES - 1) * GT_BK, (slab + GL_STAGES - 1) % GL_STAGES);
+        cp_async_commit();
+        const int buf = slab % GL_STAGES;
+#pragma unroll
+        for (int ks = 0; ks < GT_BK / 16; ++ks) {
+            uint32_t af[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ldmatrix_x4(af[i], &a_s[buf][64 * wy + 16 * i + (lane & 15)][16 * ks + (lane >> 4) * 8]);
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {
+                uint32_t wf[4];
+                ldmatrix_x4(wf, &w_s[buf][32 * wx + 16 * j2 + (lane >> 4) * 8 + (lane & 7)][16 * ks + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    mma_bf16_16816(acc[i][2 * j2], af[i], wf[0], wf[1]);
+                    mma_bf16_16816(acc[i][2 * j2 + 1], af[i], wf[2], wf[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int gm = m0 + 64 * wy + 16 * i + (lane >> 2) + 8 * half;
+            if (gm >= m_end) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int gn = n0 + 32 * wx + 8 * j + 2 * (lane & 3);
+                bf16* dst = C + (long long)gm * g.ldc + gn;
+                const float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
+                else {
+                    if (gn < N) dst[0] = __float2bfloat16_rn(v0);
+                    if (gn + 1 < N) dst[1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
 static bool mma_takes(const GroupedArgs& g) {
     const long long strides = g.lda | g.ldw | g.a_group_cols | g.w_group_stride | (long long)g.k;
     return strides % 8 == 0 && ((uintptr_t)g.a | (uintptr_t)g.w) % 16 == 0;
 }
 
+// Rows from which uniform groups take the large tile.
+#define GL_MIN_ROWS 512
+
 // See the top of the file. tile_group == null: uniform groups over all rows; else the ragged plan (a_group_cols and
-// c_group_cols are then not used). A, W and C share the activation dtype.
+// c_group_cols are then not used), whose tiles have `tile_rows` rows: 64, or 128 for the large tile (bfloat16 with aligned
+// operands only: see qf_grouped_gemm_large_takes). A, W and C share the activation dtype; a_rows: see the top.
 QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
                               long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
                               int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
-                              const int* offsets, const int* n_tiles, int max_tiles, cudaStream_t stream) {
+                              const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
+                              cudaStream_t stream) {
     if (rows <= 0 || n <= 0 || n_groups <= 0) return 0;
     GroupedArgs g{a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
-                  tile_group, tile_row0, offsets, n_tiles, max_tiles};
+                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows};
+    const bool large = tile_group ? tile_rows == GL_BM : (is_bf16 && mma_takes(g) && rows >= GL_MIN_ROWS);
+    if (tile_group && tile_rows != GL_BM && tile_rows != QF_GROUP_BM) return (int)cudaErrorInvalidValue;
+    if (large) {
+        if (!is_bf16 || !mma_takes(g)) return (int)cudaErrorInvalidValue;
+        const size_t smem = (size_t)GL_STAGES * (GL_BM + GL_BN) * GT_LD * sizeof(bf16);
+        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_mma_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        const dim3 grid((n + GL_BN - 1) / GL_BN, tile_group ? max_tiles : (rows + GL_BM - 1) / GL_BM, tile_group ? 1 : n_groups);
+        if (grid.y == 0 || grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+        return (int)launch_pdl(grouped_gemm_mma_large_kernel, grid, dim3(256), smem, stream, g);
+    }
     const dim3 grid((n + GG_BN - 1) / GG_BN, tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
     if (grid.y == 0 || grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     if (is_bf16 && mma_takes(g)) return (int)launch_pdl(grouped_gemm_mma_kernel, grid, dim3(128), 0, stream, g);
     if (is_bf16) return (int)launch_pdl(grouped_gemm_plain_kernel<bf16>, grid, dim3(256), 0, stream, g);
     return (int)launch_pdl(grouped_gemm_plain_kernel<float>, grid, dim3(256), 0, stream, g);
+}
+
+// Whether a ragged product of these operands may use tiles of 128 rows (the plan has to be cut accordingly).
+QF_EXPORT int qf_grouped_gemm_large_takes(int is_bf16, const void* a, long long lda, const void* w, long long w_group_stride,
+                                          long long ldw, int k) {
+    GroupedArgs g{a, lda, 0, w, w_group_stride, ldw, nullptr, 0, 0, 0, 0, k, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr};
+    return is_bf16 && mma_takes(g) ? 1 : 0;
 }

@@ -5,7 +5,9 @@
 //            score, the score being sigmoid(logit) or, with `softmax_scores`, the softmax over the experts; the weights
 //            are the chosen scores, divided by their sum when `renormalize` is set. The (token, expert) pairs are
 //            sorted by expert: rows offsets[e] .. offsets[e+1]-1 of the sorted order belong to expert e, and every
-//            expert's rows are cut into tiles of QF_GROUP_BM rows for the grouped product (csrc/grouped_gemm.cu).
+//            expert's rows are cut into tiles of `tile_rows` rows for the grouped product (csrc/grouped_gemm.cu).
+//            For a step of few tokens the plan can make the logits itself from the tokens' rows and the router's
+//            weights (float32 sums of the products, a warp per logit), which saves a launch where launches are the cost.
 //   gather   x_sorted[r] = x[token of r] (* weight of r, when the weight multiplies the expert's input)
 //   combine  out[t] = sum over the token's pairs, in the order of its choice, of y_sorted[row of the pair]
 //            (* weight, when the weight multiplies the expert's output), summed in float32
@@ -26,12 +28,34 @@ __global__ void __launch_bounds__(MOE_PLAN_THREADS)
 moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                 int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ sorted_token,
                 float* __restrict__ sorted_weight, int* __restrict__ dest, int* __restrict__ offsets,
-                int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles) {
+                int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles,
+                int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16,
+                float* __restrict__ logits_out) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;                   // [experts]: rows per expert, then every expert's first row
     int* first_tile = shared + n_experts;   // [experts + 1]
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    if (x) {  // the router's product first: logits_out[t][e] = sum_c x[t][c] * router[e][c], a warp per logit
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+        for (int i = warp; i < n_tokens * n_experts; i += n_warps) {
+            const int t = i / n_experts, e = i % n_experts;
+            float sum = 0.f;
+            if (x_is_bf16) {
+                const bf16* xr = (const bf16*)x + (size_t)t * width;
+                const bf16* rr = (const bf16*)router + (size_t)e * width;
+                for (int c = lane; c < width; c += 32) sum = fmaf(__bfloat162float(xr[c]), __bfloat162float(rr[c]), sum);
+            } else {
+                const float* xr = (const float*)x + (size_t)t * width;
+                const float* rr = (const float*)router + (size_t)e * width;
+                for (int c = lane; c < width; c += 32) sum = fmaf(xr[c], rr[c], sum);
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) logits_out[i] = sum;
+        }
+        logits = logits_out;
+        __threadfence_block();
+    }
     __syncthreads();
     // pass 1: choose, and take a rank among the expert's rows
     for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
@@ -75,7 +99,7 @@ moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, i
             counts[e] = row;
             first_tile[e] = tile;
             row += n;
-            tile += (n + QF_GROUP_BM - 1) / QF_GROUP_BM;
+            tile += (n + tile_rows - 1) / tile_rows;
         }
         offsets[n_experts] = row;
         first_tile[n_experts] = tile;
@@ -86,7 +110,7 @@ moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, i
         const int row0 = counts[e];
         for (int i = first_tile[e]; i < first_tile[e + 1] && i < max_tiles; ++i) {
             tile_group[i] = e;
-            tile_row0[i] = row0 + (i - first_tile[e]) * QF_GROUP_BM;
+            tile_row0[i] = row0 + (i - first_tile[e]) * tile_rows;
         }
     }
     // pass 2: every pair's row (each thread finishes the pairs it made itself)
@@ -132,19 +156,22 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
     }
 }
 
-// The most tiles any routing of `pairs` rows over `n_experts` experts can have.
-QF_EXPORT int qf_moe_max_tiles(int pairs, int n_experts) { return (pairs + QF_GROUP_BM - 1) / QF_GROUP_BM + n_experts; }
-
-// pairs = n_tokens * top: pair_expert, pair_weight (scratch), sorted_token, sorted_weight and dest have that many elements.
+// pairs = n_tokens * top: pair_expert, pair_weight (scratch), sorted_token, sorted_weight and dest have that many elements;
+// tile_group and tile_row0 max_tiles >= ceil(pairs / tile_rows) + n_experts. Either `logits` float32 [n_tokens][n_experts]
+// is given, or x [n_tokens][width] and router [n_experts][width] (both bfloat16 or both float32) with logits_out as scratch
+// for the logits the kernel then makes itself.
 QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                           int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
-                          int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, cudaStream_t stream) {
+                          int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                          const void* x, const void* router, int width, int x_is_bf16, float* logits_out, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192) return (int)cudaErrorInvalidValue;
+    if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192 || tile_rows <= 0) return (int)cudaErrorInvalidValue;
+    if (!logits && !(x && router && logits_out)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     return (int)launch_pdl(moe_plan_kernel, dim3(1), dim3(MOE_PLAN_THREADS), smem, stream, logits, n_tokens, n_experts, top,
                            softmax_scores, renormalize, pair_expert, pair_weight, sorted_token, sorted_weight, dest, offsets,
-                           tile_group, tile_row0, n_tiles, max_tiles);
+                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16,
+                           logits_out);
 }
 
 QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token, const float* sorted_weight, void* out,

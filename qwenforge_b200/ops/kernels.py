@@ -1052,13 +1052,18 @@ def latent_norm_cache(down: torch.Tensor, q_rank: int, q_norm: Optional[torch.Te
         _I(1 if write_cache else 0), _I(n), _ptr(err), _stream()), "latent_norm_cache")
 
 
-def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan) -> None:
+def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None) -> None:
     groups, n, k = weight.shape
-    _check(library("grouped_gemm").qf_grouped_gemm(
+    code = library("grouped_gemm").qf_grouped_gemm(
         _I(_is_bf16(x.dtype)), _ptr(x), _LL(x.stride(0)), _LL(a_group_cols), _ptr(weight), _LL(weight.stride(0)),
         _LL(weight.stride(1)), _ptr(out), _LL(out.stride(0)), _LL(c_group_cols), _I(rows), _I(n), _I(k), _I(groups),
         _ptr(plan.tile_group if plan else None), _ptr(plan.tile_row0 if plan else None), _ptr(plan.offsets if plan else None),
-        _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _stream()), "grouped_gemm")
+        _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _I(plan.tile_rows if plan else 0),
+        _ptr(a_rows), _stream())
+    if code == 1:
+        raise KernelError("grouped_gemm: the plan's tiles do not fit these operands (tiles of 128 rows need bfloat16 operands "
+                          "whose K and strides are multiples of 8), or the grid is too large")
+    _check(code, "grouped_gemm")
 
 
 def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -1073,7 +1078,9 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> Non
     _grouped(x, weight, out, k, n, x.shape[0], None)
 
 
-GROUP_TILE_ROWS = 64   # rows of a tile of the grouped products (QF_GROUP_BM in csrc/common.cuh)
+GROUP_TILE_ROWS = 64          # rows of a tile of the grouped products (QF_GROUP_BM in csrc/common.cuh)
+GROUP_LARGE_TILE_ROWS = 128   # and of the large tile, for bfloat16 operands with rows enough
+MOE_FUSED_ROUTER_MAX = 4096   # tokens x experts up to which the plan's one block makes the router's logits itself
 
 
 class MoePlan:
@@ -1081,10 +1088,10 @@ class MoePlan:
     sorted by expert into rows. dest[t * top + j]: the row of token t's j-th choice; sorted_token / sorted_weight: each row's
     token and routing weight; offsets: every expert's first row; tile_*: the rows cut into tiles for `expert_linear`."""
 
-    def __init__(self, n_tokens: int, n_experts: int, top: int, device):
-        self.n_tokens, self.n_experts, self.top = n_tokens, n_experts, top
+    def __init__(self, n_tokens: int, n_experts: int, top: int, device, tile_rows: int = GROUP_TILE_ROWS):
+        self.n_tokens, self.n_experts, self.top, self.tile_rows = n_tokens, n_experts, top, tile_rows
         self.pairs = pairs = n_tokens * top
-        self.max_tiles = -(-pairs // GROUP_TILE_ROWS) + n_experts   # the most tiles any routing can have
+        self.max_tiles = -(-pairs // tile_rows) + n_experts   # the most tiles any routing can have
         ints = torch.empty(3 * pairs + n_experts + 1 + 2 * self.max_tiles + 1, dtype=torch.int32, device=device)
         floats = torch.empty(2 * pairs, dtype=torch.float32, device=device)
         o = 0
@@ -1100,16 +1107,39 @@ class MoePlan:
         self.pair_weight, self.sorted_weight = floats[:pairs], floats[pairs:]
 
 
-def moe_plan(logits: torch.Tensor, top: int, softmax_scores: bool = False, renormalize: bool = False) -> MoePlan:
+def moe_tile_rows(n_tokens: int, n_experts: int, top: int, weight: torch.Tensor) -> int:
+    """The tile height for the experts' products of a step: 128 where the experts have rows enough to fill such tiles
+    (two of them each on average) and the operands allow the large tile, else 64."""
+    if weight.dtype != torch.bfloat16 or n_tokens * top < 2 * GROUP_LARGE_TILE_ROWS * n_experts:
+        return GROUP_TILE_ROWS
+    aligned = all(s % 8 == 0 for s in (weight.stride(0), weight.stride(1), weight.shape[2])) and weight.data_ptr() % 16 == 0
+    return GROUP_LARGE_TILE_ROWS if aligned else GROUP_TILE_ROWS
+
+
+def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = False, renormalize: bool = False,
+             tile_rows: int = GROUP_TILE_ROWS, x: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None) -> MoePlan:
     """Route: logits float32 [T, E] -> the `top` experts with the largest scores per token (sigmoid of the logit, or the
-    softmax over the experts) and the sorted rows (see `MoePlan`). Everything stays on the device."""
-    _dev("logits", logits, torch.float32)
-    n_tokens, n_experts = logits.shape
-    plan = MoePlan(n_tokens, n_experts, top, logits.device)
+    softmax over the experts) and the sorted rows (see `MoePlan`), cut into tiles of `tile_rows`. Everything stays on the
+    device. With `logits` None, the kernel makes the logits itself from `x` [T, W] and `router` [E, W] (float32 sums; for
+    steps of few tokens, T * E <= MOE_FUSED_ROUTER_MAX)."""
+    if logits is not None:
+        _dev("logits", logits, torch.float32)
+        n_tokens, n_experts = logits.shape
+        width, scratch = 0, None
+    else:
+        _dev("x", x)
+        _dev("router", router, x.dtype)
+        (n_tokens, width), n_experts = x.shape, router.shape[0]
+        if router.shape[1] != width or n_tokens * n_experts > MOE_FUSED_ROUTER_MAX:
+            raise KernelError("moe_plan: x [T, W] and router [E, W] with T * E <= %d, or give the logits" % MOE_FUSED_ROUTER_MAX)
+        scratch = torch.empty((n_tokens, n_experts), dtype=torch.float32, device=x.device)
+    plan = MoePlan(n_tokens, n_experts, top, (logits if logits is not None else x).device, tile_rows)
     code = library("moe").qf_moe_plan(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
                                       _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
                                       _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),
-                                      _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles), _stream())
+                                      _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
+                                      _I(tile_rows), _ptr(x if logits is None else None), _ptr(router if logits is None else None),
+                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _ptr(scratch), _stream())
     if code == 1:
         raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16, experts <= 8192)")
     _check(code, "moe_plan")
@@ -1138,13 +1168,27 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output:
            "moe_combine")
 
 
-def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor) -> None:
+def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor, gather: bool = False) -> None:
     """out[row] = x[row] @ weight[expert of the row].T for rows sorted by expert (`plan`): x [T * top, K], weight [E, N, K],
-    out [T * top, N], all of the activation dtype; one launch, no count on the host."""
+    out [T * top, N], all of the activation dtype; one launch, no count on the host. With `gather`, x is the tokens' own
+    rows [T, K] and row r reads x[token of r]: the sorted rows are never stored."""
     _dev("x", x)
     _dev("weight", weight, x.dtype)
     _dev("out", out, x.dtype)
     groups, n, k = weight.shape
-    if groups != plan.n_experts or x.shape != (plan.pairs, k) or out.shape != (plan.pairs, n):
+    if groups != plan.n_experts or x.shape != ((plan.n_tokens if gather else plan.pairs), k) or out.shape != (plan.pairs, n):
         raise KernelError(f"expert_linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
-    _grouped(x, weight, out, 0, 0, plan.pairs, plan)
+    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None)
+
+
+def scaled_swiglu(gate_up: torch.Tensor, row_scale: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, i] = silu(s_r * gate_up[r, i]) * (s_r * gate_up[r, I + i]): SwiGLU of rows whose input was to be multiplied by
+    s_r (float32 [rows]), on the product of the unscaled rows."""
+    _dev("gate_up", gate_up)
+    _dev("row_scale", row_scale, torch.float32)
+    _dev("out", out, gate_up.dtype)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or row_scale.numel() != rows:
+        raise KernelError("scaled_swiglu: out must be [rows, width / 2], row_scale [rows]")
+    _check(library("activation").qf_scaled_swiglu(_I(_is_bf16(gate_up.dtype)), _ptr(gate_up), _ptr(row_scale), _ptr(out),
+                                                  _I(rows), _I(two_i // 2), _stream()), "scaled_swiglu")

@@ -66,3 +66,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             torch.addmm(bias, x, weight.t(), out=out)
         return out
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def linear_rows(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """`linear` without a bias for parts whose steps may have few rows: up to 16 bfloat16 rows run on this library's
+    weight streamer where it takes the shape and is the faster way (`skinny_gemm_takes`, `skinny_gemm_pays`). Unlike
+    the library product it is launched as a programmatic dependent, so a chain of such products and the small kernels
+    between them runs without gaps: the kernel after it starts its weight copies under this one's tail. Everything else
+    goes to `linear`. The result is bfloat16, or float32 with `out_dtype=torch.float32`."""
+    m = x.shape[0]
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and m <= kernels.SKINNY_MAX_ROWS and x.stride(1) == 1
+            and kernels.skinny_gemm_takes(m, weight, kernels.EPI_PLAIN, False, ldx=x.stride(0)) and kernels.skinny_gemm_pays(m, weight)):
+        out = torch.empty((m, weight.shape[0]), device=x.device, dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16)
+        kernels.skinny_gemm(kernels.EPI_PLAIN, weight, x=x, out=out)
+        return out
+    return linear(x, weight, None, out_dtype=out_dtype)

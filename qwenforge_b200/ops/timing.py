@@ -16,7 +16,9 @@ import torch
 
 TIMED = ("embed_gather", "gather_rows", "add_rms_norm", "residual_add", "linear", "gemm_f32", "rope_cache_write",
          "attention_generic", "attention_prefill", "attention_prefill_tc", "attention_decode", "swiglu", "skinny_gemm",
-         "tc_gemm", "sample", "decode_advance")
+         "tc_gemm", "sample", "decode_advance", "wide_gemm", "fold_project", "gather_rows_norm", "embed_positions",
+         "sandwich_norm", "clamped_glu", "latent_norm_cache", "head_linear", "expert_linear", "moe_plan", "moe_gather",
+         "moe_combine")
 
 
 class KernelTimer:

@@ -6,6 +6,7 @@
   out = sum_e expert_e(w_e * h)             `weight_on` = "input": the weight multiplies what the expert reads
      or sum_e w_e * expert_e(h)             `weight_on` = "output"
   expert(v) = D_e (silu(G_e v) * (U_e v)),  no biases
+(computed as silu(w_e (G_e h)) * (w_e (U_e h)) for a weight on the input: the same numbers, the scale applied to float32 sums)
 
 Routing, sorting by expert and the experts' products all stay on the device (`ops.moe_plan`, `ops.expert_linear`: one
 launch per product for all experts, sized by what any routing can need), so the part is graph safe: a decode graph
@@ -63,14 +64,23 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         # float32 logits from the rows as the experts see them (their bfloat16 rounding on the 16-bit path: products of
         # bfloat16 numbers are exact in float32, and the sums are float32)
-        logits = ops.linear(x, self.router, out_dtype=torch.float32)
-        plan = ops.moe_plan(logits, self.top, self.score == "softmax", self.renormalize)
-        rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
-        ops.moe_gather(x, plan, rows, self.weight_on == "input")
+        n = x.shape[0]
+        tile_rows = ops.moe_tile_rows(n, self.n_experts, self.top, self.gate_up)
+        soft, renorm = self.score == "softmax", self.renormalize
+        if n * self.n_experts <= ops.MOE_FUSED_ROUTER_MAX:
+            plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router)   # few tokens: one launch
+        else:
+            plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows)
+        # The sorted rows are read through the plan's row map and never stored. A weight on the expert's input moves
+        # behind its first product (G (w h) = w (G h), and the same for U), where it meets float32 sums.
         gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
-        ops.expert_linear(rows, self.gate_up, plan, gate_up)
+        ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
         act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
-        ops.swiglu(gate_up, act)
+        if self.weight_on == "input":
+            ops.scaled_swiglu(gate_up, plan.sorted_weight, act)
+        else:
+            ops.swiglu(gate_up, act)
+        rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
         ops.expert_linear(act, self.down, plan, rows)
         out = torch.empty_like(x)
         ops.moe_combine(rows, plan, out, self.weight_on == "output")

@@ -32,7 +32,7 @@ class ClampedGlu(FeedForward):
         ]
 
     def kernel_libraries(self, dtype):
-        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else set())
+        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm"})
 
     def bind(self, tensors, dtype, device):
         self.gate_up_weight = torch.cat((tensors[self.file_name("gate_weight")], tensors[self.file_name("up_weight")]),
@@ -44,8 +44,8 @@ class ClampedGlu(FeedForward):
 
     def forward(self, x, ctx):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.clamped_glu(ops.linear(x, self.gate_up_weight), self.limit, self.alpha, act)
-        return ops.linear(act, self.down_weight)
+        ops.clamped_glu(ops.linear_rows(x, self.gate_up_weight), self.limit, self.alpha, act)
+        return ops.linear_rows(act, self.down_weight)
 
 
 register_part("feed_forward", "clamped_glu", ClampedGlu)

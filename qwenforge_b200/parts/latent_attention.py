@@ -96,15 +96,15 @@ class LatentAttention(Mixer):
     def _latents(self, x, ctx, args, writes_cache):
         """The queries of the step's tokens, [T, H * dim], after the key/value latents went into the cache."""
         n = x.shape[0]
-        down = ops.linear(x, self.down_weight, out_dtype=torch.float32)
+        down = ops.linear_rows(x, self.down_weight, out_dtype=torch.float32)
         if not self.q_rank:
             ops.latent_norm_cache(down, 0, None, self.kv_norm, self.eps, ctx.tok_seq, ctx.tok_pos, ctx.slots, None, args,
                                   writes_cache, ctx.err)
-            return ops.linear(x, self.q_up)
+            return ops.linear_rows(x, self.q_up)
         q_latent = torch.empty((n, self.q_rank), dtype=x.dtype, device=x.device)
         ops.latent_norm_cache(down, self.q_rank, self.q_norm, self.kv_norm, self.eps, ctx.tok_seq, ctx.tok_pos, ctx.slots,
                               q_latent, args, writes_cache, ctx.err)
-        return ops.linear(q_latent, self.q_up)
+        return ops.linear_rows(q_latent, self.q_up)
 
     def forward(self, x, ctx, site, writes_cache):
         n, h, r = x.shape[0], self.n_heads, self.kv_rank
@@ -129,7 +129,7 @@ class LatentAttention(Mixer):
                                   sinks=self.sinks, shared_values=True)
         values = torch.empty((n, h * self.value_dim), dtype=x.dtype, device=x.device)
         ops.head_linear(attended, self.v_up, values)
-        return ops.linear(values, self.o_weight)
+        return ops.linear_rows(values, self.o_weight)
 
     def decode_plan(self, ctx, n_splits: int) -> torch.Tensor:
         """The decode attention's plan of this step, shared through the step's memo by every layer of this shape."""

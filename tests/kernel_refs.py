@@ -212,7 +212,23 @@ class _Routing:
     pass
 
 
-def moe_plan(logits, top, softmax_scores=False, renormalize=False):
+def linear_rows(x, weight, out_dtype=None):
+    return linear(x, weight, None, out_dtype=out_dtype)
+
+
+def moe_tile_rows(n_tokens, n_experts, top, weight):
+    return 64
+
+
+def scaled_swiglu(gate_up, row_scale, out):
+    inter = gate_up.shape[1] // 2
+    g, u = _f(gate_up[:, :inter]) * _f(row_scale)[:, None], _f(gate_up[:, inter:]) * _f(row_scale)[:, None]
+    out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+
+
+def moe_plan(logits, top, softmax_scores=False, renormalize=False, tile_rows=64, x=None, router=None):
+    if logits is None:
+        logits = (_f(x) @ _f(router).T)
     z = logits.to(torch.float32)
     scores = torch.softmax(z, -1) if softmax_scores else torch.sigmoid(z)
     chosen = torch.topk(scores, top, dim=-1)
@@ -243,11 +259,12 @@ def moe_combine(y, plan, out, scale_output):
     out.copy_(rows[plan.dest.long()].view(plan.n_tokens, plan.top, -1).sum(1).to(out.dtype))
 
 
-def expert_linear(x, weight, plan, out):
-    out.copy_(torch.einsum("rk,rnk->rn", _f(x), _f(weight)[plan.row_expert]).to(out.dtype))
+def expert_linear(x, weight, plan, out, gather=False):
+    rows = _f(x)[plan.sorted_token.long()] if gather else _f(x)
+    out.copy_(torch.einsum("rk,rnk->rn", rows, _f(weight)[plan.row_expert]).to(out.dtype))
 
 
-ALL = dict(embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
+ALL = dict(linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
            head_linear=head_linear, moe_plan=moe_plan, moe_gather=moe_gather, moe_combine=moe_combine, expert_linear=expert_linear,
            embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
            linear=linear, rope_cache_write=rope_cache_write, attention_generic=attention_generic, swiglu=swiglu,

@@ -117,6 +117,25 @@ def layer(weights, config: dict, index: int, x: torch.Tensor, latents_before=Non
     return x, latents
 
 
+def router_margins(config: dict, weights, tokens) -> torch.Tensor:
+    """Per token, the smallest gap over all routed layers between the last chosen expert's logit and the first one left
+    out, relative to the token's largest logit there (inf without routed layers). A token whose margin is below the
+    rounding of a 16-bit path may rightly be routed otherwise there."""
+    x = embed(weights, tokens)
+    eps = float(config["norm"]["eps"])
+    margins = torch.full((len(tokens),), math.inf, dtype=F)
+    for i, spec in enumerate(config["layers"]):
+        mlp, p = spec.get("mlp"), f"l{i}."
+        if mlp is not None and mlp["kind"] == "moe" and mlp["router"]["top"] < mlp["router"]["experts"]:
+            mixed, _ = latent_attention(weights, p + "mix.", spec["mixer"], rms(x, weights[p + "norm1"].to(F), eps), eps)
+            h = rms(x + rms(mixed, weights[p + "norm1b"].to(F), eps), weights[p + "norm2"].to(F), eps)
+            z = torch.sort(h @ weights[p + "mlp.router"].to(F).T, dim=-1, descending=True).values
+            top = mlp["router"]["top"]
+            margins = torch.minimum(margins, (z[:, top - 1] - z[:, top]) / z.abs().max(-1).values)
+        x, _ = layer(weights, config, i, x)
+    return margins
+
+
 def logits_of(weights, config: dict, x: torch.Tensor) -> torch.Tensor:
     return rms(x, weights["final.norm"].to(F), float(config["norm"]["eps"])) @ weights["head"].to(F).T
 
