@@ -357,7 +357,8 @@ DESIGN_PAIRS = {"mefepel": [("mefepel-0.5b", "qwen2.5-0.5b", None), ("mefepel-3b
 # what a kernel's label (ops/timing.py) counts as, so that like is laid beside like
 KERNEL_KINDS = (("attention_prefill", "attention (prompt)"), ("attention_decode", "attention (decode)"),
                 ("attention_generic", "attention (plain)"), ("head_linear", "per-head products"),
-                ("expert_linear", "expert products"), ("moe_", "routing"), ("linear", "library products"),
+                ("expert_linear", "expert products"), ("tc_gemm_grouped", "expert products"), ("scaled_swiglu", "gates"),
+                ("linear_rows", "products of the step's rows"), ("moe_", "routing"), ("linear", "library products"),
                 ("tc_gemm", "own tcgen05 product"), ("skinny_gemm", "skinny products"), ("wide_gemm", "wide products"),
                 ("fold_project", "fold + output projection"), ("norm", "norms"), ("residual_add", "norms"),
                 ("rope_cache_write", "rotation + cache write"), ("latent_norm_cache", "latent norms + cache write"),

@@ -71,6 +71,22 @@ __device__ __forceinline__ void qkv_head_turn(uint32_t lane_addr, int col, int P
     }
 }
 
+// Grouped products (the experts of a mixture-of-experts feed-forward): the rows of A are sorted by group and cut into tiles
+// of 128 rows by a plan on the device (csrc/moe.cu). Tile i belongs to group tile_group[i], starts at row tile_row0[i] (any
+// row: a tiled copy's row coordinate has no alignment rule) and ends where the group's rows end; what the tile holds beyond
+// that end are the next group's rows, which are multiplied and not stored. Group g's weights are rows g * w_rows .. of W.
+// The grid has a block row for every tile that any routing can have; those beyond n_tiles[0] end at once. `row_scale`
+// (float32 per row, or null) multiplies both halves of the TC_SWIGLU epilogue's sums before the gate: a weight on the
+// expert's input moved behind its first product. tile_group == null: an ordinary product.
+struct TcGroups {
+    const int* tile_group;
+    const int* tile_row0;
+    const int* offsets;
+    const int* n_tiles;
+    const float* row_scale;
+    int w_rows;
+};
+
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 128
@@ -89,7 +105,8 @@ template <int BN> __device__ __forceinline__ constexpr uint32_t tc_idesc() {
 template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, bf16* __restrict__ out,
-               int M, int n_out, int K, int inter, int ldo, const TcQkvArgs qa, int* err) {
+               int M, int n_out, int K, int inter, int ldo, const TcQkvArgs qa, int* err, const TcGroups gr) {
+    if (gr.tile_group && (int)blockIdx.y >= gr.n_tiles[0]) return;   // the whole block, before it holds anything
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     constexpr int TC_STAGES = TcGeometry<BN>::stages, TC_STAGE_BYTES = TcGeometry<BN>::stage_bytes;
@@ -100,6 +117,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int n_k = (K + TC_BK - 1) / TC_BK;
+    const int group = gr.tile_group ? gr.tile_group[blockIdx.y] : 0;
+    const int row0 = gr.tile_group ? gr.tile_row0[blockIdx.y] : tile_m * TC_BM;   // first row of the tile
+    const int row_end = gr.tile_group ? min(gr.offsets[group + 1], M) : M;       // rows from here on are not this tile's
+    const int w_row0 = gr.tile_group ? group * gr.w_rows : 0;                     // first weight row of the tile's group
     // TC_QKV: where this thread's token row stands and where its key and value go (element offset in the cache, -1: nowhere)
     long long kv_at = -1;
     auto find_row = [&]() {
@@ -142,13 +163,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned char* a_s = smem + (size_t)s * TC_STAGE_BYTES;
             unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
             mbar_expect_tx(&full_bar[s], TC_STAGE_BYTES);
-            tma_load_2d(a_s, &map_a, kb * TC_BK, tile_m * TC_BM, &full_bar[s]);
+            tma_load_2d(a_s, &map_a, kb * TC_BK, row0, &full_bar[s]);
 #pragma unroll
             for (int box = 0; box < BN / 64; ++box) {  // boxes of 64 weight rows
                 int w_row = tile_n * BN + 64 * box;
                 if (EPI == TC_SWIGLU)  // HALF gate rows, then the HALF matching up rows
                     w_row = 64 * box < HALF ? tile_n * HALF + 64 * box : inter + tile_n * HALF + (64 * box - HALF);
-                tma_load_2d(b_s + (size_t)box * 64 * TC_BK * 2, &map_b, kb * TC_BK, w_row, &full_bar[s]);
+                tma_load_2d(b_s + (size_t)box * 64 * TC_BK * 2, &map_b, kb * TC_BK, w_row0 + w_row, &full_bar[s]);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -184,7 +205,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- epilogue: warp w owns accumulator lanes (= tile rows) 32 w .. 32 w + 31
     if (!mbar_wait(&acc_bar, 0) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
     tc_fence_after();
-    const int row = tile_m * TC_BM + warp * 32 + lane;
+    const int row = row0 + warp * 32 + lane;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
     if (EPI == TC_QKV) {
         __syncthreads();  // the tile's bias values are in shared memory
@@ -214,13 +235,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tmem_load_32(lane_base + c0, g);
             tmem_load_32(lane_base + HALF + c0, u);
             const int col = tile_n * HALF + c0;
-            if (row < M && col < n_out) {
+            if (row < row_end && col < n_out) {
+                const float rs = gr.row_scale ? gr.row_scale[row] : 1.0f;
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-                    packed[j] = pack_bf16(g0 / (1.0f + expf(-g0)) * __uint_as_float(u[2 * j]),
-                                          g1 / (1.0f + expf(-g1)) * __uint_as_float(u[2 * j + 1]));
+                    const float g0 = rs * __uint_as_float(g[2 * j]), g1 = rs * __uint_as_float(g[2 * j + 1]);
+                    packed[j] = pack_bf16(g0 / (1.0f + expf(-g0)) * (rs * __uint_as_float(u[2 * j])),
+                                          g1 / (1.0f + expf(-g1)) * (rs * __uint_as_float(u[2 * j + 1])));
                 }
                 bf16* dst = out + (size_t)row * ldo + col;
                 if (col + 32 <= n_out) {
@@ -238,7 +260,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t v[32];
             tmem_load_32(lane_base + c0, v);
             const int col = tile_n * BN + c0;
-            if (row < M && col < n_out) {
+            if (row < row_end && col < n_out) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) packed[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
@@ -472,8 +494,41 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* o
     const size_t smem = TcGeometry<BN>::smem;
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, TcQkvArgs{}, err);
+    tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, TcQkvArgs{}, err,
+                                                                TcGroups{});
     return (int)cudaGetLastError();
+}
+
+template <int EPI>
+static int launch_tc_grouped(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n_out, int k, int inter, int ldo,
+                             int* err, dim3 grid, const TcGroups& groups, cudaStream_t stream) {
+    const size_t smem = TcGeometry<128>::smem;
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<EPI, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    tc_gemm_kernel<EPI, 128><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, TcQkvArgs{}, err, groups);
+    return (int)cudaGetLastError();
+}
+
+// The grouped form (see TcGroups): a [m][lda] rows sorted by group, w [n_groups * n][ldw] the groups' weights one after the
+// other (n rows each; TC_SWIGLU: n = 2 * inter, a group's gate rows then its up rows), out [m][ldo] with n columns
+// (TC_SWIGLU: inter). The plan's tiles have 128 rows; max_tiles bounds their number. The conditions of qf_tc_gemm hold.
+QF_EXPORT int qf_tc_gemm_grouped(int epilogue, const void* a, int lda, const void* w, int ldw, int n_groups, void* out, int ldo,
+                                 int m, int n, int k, const int* tile_group, const int* tile_row0, const int* offsets,
+                                 const int* n_tiles, int max_tiles, const float* row_scale, int* err, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || n_groups <= 0) return 0;
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8 || ldo % 8 || !tile_group || max_tiles <= 0 || max_tiles > 65535) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b;
+    if (!qf_make_map_bf16(&map_a, a, m, k, lda, TC_BM) || !qf_make_map_bf16(&map_b, w, (long long)n_groups * n, k, ldw, 64))
+        return (int)cudaErrorNotSupported;
+    TcGroups groups{tile_group, tile_row0, offsets, n_tiles, row_scale, n};
+    if (epilogue == TC_SWIGLU) {
+        if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
+        const int inter = n / 2;
+        return launch_tc_grouped<TC_SWIGLU>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 63) / 64, max_tiles), groups, stream);
+    }
+    if (epilogue != TC_PLAIN || row_scale) return (int)cudaErrorInvalidValue;
+    return launch_tc_grouped<TC_PLAIN>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, max_tiles), groups, stream);
 }
 
 static int g_persistent = 1;
@@ -542,6 +597,6 @@ QF_EXPORT int qf_tc_gemm_qkv(const void* a, int lda, const void* w, int ldw, int
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_QKV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((n + 127) / 128, (m + TC_BM - 1) / TC_BM);
-    tc_gemm_kernel<TC_QKV, 128><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, nullptr, m, n, k, 0, 0, q, err);
+    tc_gemm_kernel<TC_QKV, 128><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, nullptr, m, n, k, 0, 0, q, err, TcGroups{});
     return (int)cudaGetLastError();
 }

@@ -1192,3 +1192,42 @@ def scaled_swiglu(gate_up: torch.Tensor, row_scale: torch.Tensor, out: torch.Ten
         raise KernelError("scaled_swiglu: out must be [rows, width / 2], row_scale [rows]")
     _check(library("activation").qf_scaled_swiglu(_I(_is_bf16(gate_up.dtype)), _ptr(gate_up), _ptr(row_scale), _ptr(out),
                                                   _I(rows), _I(two_i // 2), _stream()), "scaled_swiglu")
+
+
+def tc_gemm_grouped_takes(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, epilogue: int = TC_PLAIN) -> bool:
+    """Whether `tc_gemm_grouped` takes these operands: bfloat16, a plan cut into tiles of 128 rows, K and the strides
+    multiples of 8, 16-byte aligned bases, and for TC_SWIGLU an expert size that is a multiple of 8."""
+    if plan.tile_rows != GROUP_LARGE_TILE_ROWS or weight.dim() != 3 or not weight.is_contiguous() or plan.max_tiles > 65535:
+        return False
+    if epilogue == TC_SWIGLU and (weight.shape[1] % 2 or (weight.shape[1] // 2) % 8):
+        return False
+    return tc_gemm_takes(x, weight.view(-1, weight.shape[2]))
+
+
+def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor,
+                    row_scale: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> None:
+    """The experts' products on the tcgen05 tensor cores: out[row] = x[row] @ weight[expert of the row].T for rows sorted by
+    expert (`plan`, tiles of 128 rows); x [T * top, K], weight [E, N, K], out [T * top, N]. TC_SWIGLU: weight[e] = [gate rows |
+    up rows], out [T * top, N / 2] = silu(s g) * (s u) with s = row_scale[row] (float32, or 1 when None)."""
+    _dev("x", x, torch.bfloat16, contiguous=False)
+    _dev("weight", weight, torch.bfloat16)
+    _dev("out", out, torch.bfloat16, contiguous=False)
+    groups, n, k = weight.shape
+    cols = n // 2 if epilogue == TC_SWIGLU else n
+    if x.shape != (plan.pairs, k) or out.shape != (plan.pairs, cols) or groups != plan.n_experts or out.stride(1) != 1:
+        raise KernelError(f"tc_gemm_grouped: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
+    if not tc_gemm_grouped_takes(x, weight, plan, epilogue) or out.stride(0) % 8 or out.data_ptr() % 16:
+        raise KernelError("tc_gemm_grouped: operands must be bf16 with K and row strides multiples of 8, 16-byte aligned, and the "
+                          "plan cut into tiles of 128 rows")
+    if row_scale is not None:
+        _dev("row_scale", row_scale, torch.float32)
+        if row_scale.numel() != plan.pairs or epilogue != TC_SWIGLU:
+            raise KernelError("tc_gemm_grouped: row_scale is one float32 per row, for TC_SWIGLU")
+    err = err if err is not None else _err_word_for(x.device)
+    code = library("tc_gemm").qf_tc_gemm_grouped(
+        _I(epilogue), _ptr(x), _I(x.stride(0)), _ptr(weight), _I(weight.stride(1)), _I(groups), _ptr(out), _I(out.stride(0)),
+        _I(plan.pairs), _I(n), _I(k), _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.offsets), _ptr(plan.n_tiles),
+        _I(plan.max_tiles), _ptr(row_scale), _ptr(err), _stream())
+    if code == 801:
+        raise KernelError("tc_gemm_grouped: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
+    _check(code, "tc_gemm_grouped")

@@ -50,7 +50,7 @@ class RoutedExperts(FeedForward):
         return specs
 
     def kernel_libraries(self, dtype):
-        return {"activation", "moe", "grouped_gemm"} | ({"gemm_f32"} if dtype == torch.float32 else set())
+        return {"activation", "moe", "grouped_gemm"} | ({"gemm_f32"} if dtype == torch.float32 else {"tc_gemm"})
 
     def bind(self, tensors, dtype, device):
         t = lambda logical: tensors[self.file_name(logical)]
@@ -71,16 +71,29 @@ class RoutedExperts(FeedForward):
             plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router)   # few tokens: one launch
         else:
             plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows)
-        # The sorted rows are read through the plan's row map and never stored. A weight on the expert's input moves
-        # behind its first product (G (w h) = w (G h), and the same for U), where it meets float32 sums.
+        # A weight on the expert's input moves behind its first product (G (w h) = w (G h), and the same for U), where it
+        # meets float32 sums.
+        on_input = self.weight_on == "input"
+        act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
+        rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
+        if tile_rows == ops.kernels.GROUP_LARGE_TILE_ROWS and ops.tc_gemm_grouped_takes(rows, self.gate_up, plan, ops.TC_SWIGLU) \
+                and ops.tc_gemm_grouped_takes(act, self.down, plan):
+            # long steps: both products on the tcgen05 tensor cores, the gate in the first one's epilogue (its tiled copies
+            # want the sorted rows in memory, so they are gathered first)
+            ops.moe_gather(x, plan, rows, False)
+            ops.tc_gemm_grouped(ops.TC_SWIGLU, rows, self.gate_up, plan, act, plan.sorted_weight if on_input else None, ctx.err)
+            y = torch.empty_like(rows)
+            ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
+            out = torch.empty_like(x)
+            ops.moe_combine(y, plan, out, not on_input)
+            return out
+        # otherwise the sorted rows are read through the plan's row map and never stored
         gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
         ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
-        act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
-        if self.weight_on == "input":
+        if on_input:
             ops.scaled_swiglu(gate_up, plan.sorted_weight, act)
         else:
             ops.swiglu(gate_up, act)
-        rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
         ops.expert_linear(act, self.down, plan, rows)
         out = torch.empty_like(x)
         ops.moe_combine(rows, plan, out, self.weight_on == "output")

@@ -220,6 +220,16 @@ def moe_tile_rows(n_tokens, n_experts, top, weight):
     return 64
 
 
+def tc_gemm_grouped(epilogue, x, weight, plan, out, row_scale=None, err=None):
+    y = torch.einsum("rk,rnk->rn", _f(x), _f(weight)[plan.row_expert])
+    if epilogue == 1:   # gate rows then up rows, a scale on both before the gate
+        inter = y.shape[1] // 2
+        s = _f(row_scale)[:, None] if row_scale is not None else 1.0
+        g, u = y[:, :inter] * s, y[:, inter:] * s
+        y = g * torch.sigmoid(g) * u
+    out.copy_(y.to(out.dtype))
+
+
 def scaled_swiglu(gate_up, row_scale, out):
     inter = gate_up.shape[1] // 2
     g, u = _f(gate_up[:, :inter]) * _f(row_scale)[:, None], _f(gate_up[:, inter:]) * _f(row_scale)[:, None]

@@ -37,10 +37,15 @@ def logits_close(got, want, dtype, what="", margins=None):
     if dtype == torch.float32:
         assert float(err.max()) <= 1e-4, f"{what}: worst row {float(err.max()):.3e} exceeds 1e-4"
         return
+    # (A row routed otherwise also moves the few later rows whose attention hangs on it, in the layers above: so even among
+    # the clearly routed rows a few in a hundred may be far off, while the typical row is well within rounding.)
+    assert bool(torch.isfinite(err).all())
     clear = err if margins is None else err[margins > 0.03]
     assert clear.numel() >= 0.6 * err.numel()
-    assert float(clear.max()) <= 0.15 and float(clear.median()) <= 0.035, \
-        f"{what}: worst clearly routed row {float(clear.max()):.3e}, median {float(clear.median()):.3e}"
+    far_off = float((clear > 0.15).double().mean())
+    limit = 0.0 if margins is None or not bool(torch.isfinite(margins).any()) else 0.03
+    assert far_off <= limit and float(clear.median()) <= 0.035, \
+        f"{what}: {far_off:.1%} of the clearly routed rows over 0.15 (worst {float(clear.max()):.3e}), median {float(clear.median()):.3e}"
 
 
 # ------------------------------------------------------------------------------------------------ kernels alone
@@ -171,6 +176,41 @@ def test_routing_and_expert_products(dtype, shape):
     out = torch.empty(tokens, width, dtype=dtype, device=DEV)
     ops.moe_combine(y, plan, out, False)
     close(out, y.double()[dest.to(DEV)].view(tokens, top, width).sum(1), dtype, "combined")
+
+
+@pytest.mark.parametrize("shape", [(1500, 4, 2, 128, 72), (900, 3, 1, 200, 136), (2100, 5, 3, 320, 64)])
+def test_expert_products_on_tcgen05(shape):
+    """The grouped form of the tcgen05 product: tiles that start at any row and end with their expert, experts whose size is
+    no multiple of a tile's columns, the gate (with the rows' scale) in the first product's epilogue."""
+    from qwenforge_b200 import ops
+    tokens, experts, top, width, ff = shape
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(sum(shape))
+    logits = torch.randn(tokens, experts, generator=g)
+    logits[:, 0] -= 30.0
+    logits = logits.to(DEV)
+    x = torch.randn(tokens, width, generator=g).to(dtype).to(DEV)
+    w1 = (torch.randn(experts, 2 * ff, width, generator=g) / math.sqrt(width)).to(dtype).to(DEV)
+    w2 = (torch.randn(experts, width, ff, generator=g) / math.sqrt(ff)).to(dtype).to(DEV)
+    plan = ops.moe_plan(logits, top, tile_rows=128)
+    want_plan = refs.moe_plan(logits.cpu(), top)
+    offsets = plan.offsets.cpu().tolist()
+    row_expert = torch.empty(plan.pairs, dtype=torch.long)
+    for e in range(experts):
+        row_expert[offsets[e]:offsets[e + 1]] = e
+    rows = torch.empty(plan.pairs, width, dtype=dtype, device=DEV)
+    ops.moe_gather(x, plan, rows, False)
+    assert ops.tc_gemm_grouped_takes(rows, w1, plan, ops.TC_SWIGLU)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    act = torch.full((plan.pairs, ff), 7.0, dtype=dtype, device=DEV)
+    ops.tc_gemm_grouped(ops.TC_SWIGLU, rows, w1, plan, act, plan.sorted_weight, err)
+    gu = torch.einsum("rk,rnk->rn", rows.double(), w1.double()[row_expert.to(DEV)]) * plan.sorted_weight.double()[:, None]
+    want_act = gu[:, :ff] * torch.sigmoid(gu[:, :ff]) * gu[:, ff:]
+    close(act, want_act, dtype, "gate in the epilogue")
+    y = torch.full((plan.pairs, width), 7.0, dtype=dtype, device=DEV)
+    ops.tc_gemm_grouped(ops.TC_PLAIN, act, w2, plan, y, None, err)
+    close(y, torch.einsum("rk,rnk->rn", act.double(), w2.double()[row_expert.to(DEV)]), dtype, "down product")
+    assert int(err) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -416,6 +456,17 @@ def test_unequal_batches_against_each_alone_in_reused_slots(name, dtype, tmp_pat
     assert cache.slots.n_free == cache.max_seqs
 
 
+def test_a_long_prompt_takes_the_tensor_core_experts(tmp_path):
+    """1,600 tokens over four experts: tiles of 128 rows, both expert products on tcgen05, against the plain implementation."""
+    cfg = config(300, 128, 1700, 1e-5, [layer(mixer(4, 16, 16, 64, 48), moe(64, 4, 2)), layer(mixer(4, 16, 16, 64, 48), dense(160, 2.0))])
+    model, weights, _ = build(cfg, tmp_path, "bfloat16", seed=4)
+    tokens = random_tokens(cfg["vocab"], 1600, 8)
+    cache = model.new_cache(64 * 30, 2)
+    got = run_cuts(model, cache, tokens, [1600])
+    want = plain.forward_logits(cfg, weights, tokens)
+    logits_close(got[::7], want[::7], torch.bfloat16, "long prompt", plain.router_margins(cfg, weights, tokens)[::7])
+
+
 def _far_key_model(kind):
     """One layer whose attention is made to hang on ONE far position: queries and keys are scaled up, so that a key that is
     lost, shifted by one or read from the wrong page changes the logits by far more than rounding."""
@@ -426,7 +477,8 @@ def _far_key_model(kind):
 @pytest.mark.parametrize("kind", ["fast", "generic"])
 def test_far_keys_and_page_borders_show_in_the_logits(kind, dtype, tmp_path):
     cfg = _far_key_model(kind)
-    model, weights, folder = build(cfg, tmp_path, dtype, seed=12, spread=3.0)    # wide matrices: a peaked attention
+    # wide matrices: a peaked attention (less so in bfloat16, where scores of several tens carry their rounding into the weights)
+    model, weights, folder = build(cfg, tmp_path, dtype, seed=12, spread=3.0 if dtype == "float32" else 1.5)
     torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
     tokens = random_tokens(cfg["vocab"], 1100, 9)
     want = plain.forward_logits(cfg, weights, tokens)
@@ -463,3 +515,70 @@ def test_long_decoding_through_graphs_and_the_entry_point(dtype, tmp_path):
     # a second call runs in the slots and pages of the first
     again = engine.generate_ids(prompts, max_new_tokens=n_new, batch_size=2, ignore_eos=True)
     assert again == got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_user_runs_it(dtype, tmp_path):
+    """bin/trace_run in a process of its own: whole prompts, a prompt and then its last tokens one by one, and a batch of
+    unequal requests decoded together whose shorter members end earlier; requests that end give their slots back."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    cfg = MEF_ODD
+    folder, weights = make_model_dir(cfg, 31, tmp_path / "model")
+    vocab = cfg["vocab"]
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    requests = {f"q{i}": random_tokens(vocab, n, 70 + i) for i, n in enumerate((90, 1, 40, 130))}
+    want = {k: plain.forward_logits(cfg, weights, v) for k, v in requests.items()}
+    margins = {k: plain.router_margins(cfg, weights, v) for k, v in requests.items()}
+
+    def run(steps, out_dir, max_tokens):
+        text = "".join(json.dumps(s) + "\n" for s in steps)
+        done = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+                               "--out", str(out_dir), "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True, timeout=900)
+        assert done.returncode == 0, done.stderr[-2000:]
+        assert [line for line in done.stdout.splitlines() if line.startswith("done ")] == [f"done {s['step']}" for s in steps]
+
+    def read(out_dir, step):
+        return torch.from_numpy(np.fromfile(Path(out_dir) / f"{step}.f32", dtype="<f4").reshape(-1, vocab).copy())
+
+    # whole, one after the other in one process: at most 130 tokens are live at any time
+    steps = [dict(step=i, entries=[dict(id=k, tokens=v, want=list(range(len(v))))], end=[k]) for i, (k, v) in enumerate(requests.items())]
+    run(steps, tmp_path / "whole", 130)
+    for i, k in enumerate(requests):
+        if len(requests[k]) > 8:
+            logits_close(read(tmp_path / "whole", i), want[k], torch_dtype, f"whole {k}", margins[k])
+    # a prompt, then its last 20 tokens one by one; the step that wants nothing writes no file
+    k, v = "q3", requests["q3"]
+    head = len(v) - 20
+    steps = [dict(step=0, entries=[dict(id=k, tokens=v[:head], want=[])], end=[])]
+    steps += [dict(step=1 + t, entries=[dict(id=k, tokens=[v[head + t]], want=[0])], end=[k] if t == 19 else []) for t in range(20)]
+    run(steps, tmp_path / "tail", 130)
+    assert not (tmp_path / "tail" / "0.f32").exists()
+    tail = torch.cat([read(tmp_path / "tail", 1 + t) for t in range(20)])
+    logits_close(tail, want[k][head:], torch_dtype, "last tokens one by one", margins[k][head:])
+    # three requests start together (the lengths differ), are decoded together, and the shorter ones end earlier
+    cut = {"q0": 85, "q1": 1, "q2": 33}
+    steps = [dict(step=0, entries=[dict(id=k, tokens=requests[k][:n], want=[n - 1]) for k, n in cut.items()], end=["q1"])]
+    fed, live, n = dict(cut), ["q0", "q2"], 1
+    got = {k: [] for k in cut}
+    order = {0: list(cut)}
+    while live:
+        steps.append(dict(step=n, entries=[dict(id=k, tokens=[requests[k][fed[k]]], want=[0]) for k in live],
+                          end=[k for k in live if fed[k] + 1 == len(requests[k])]))
+        order[n] = list(live)
+        for k in live:
+            fed[k] += 1
+        live = [k for k in live if fed[k] < len(requests[k])]
+        n += 1
+    run(steps, tmp_path / "batch", 85 + 1 + 33 + 12)
+    for step, names in order.items():
+        rows = read(tmp_path / "batch", step)
+        for row, k in zip(rows, names):
+            got[k].append(row)
+    for k in ("q0", "q2"):
+        logits_close(torch.stack(got[k]), want[k][cut[k] - 1:], torch_dtype, f"batch {k}", margins[k][cut[k] - 1:])
