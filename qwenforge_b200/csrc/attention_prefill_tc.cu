@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(TA_THREADS, D > 64 ? 2 : 3)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   bf16* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                   const int* __restrict__ slots, KvSite<bf16> site, int n_heads, int n_seqs, int row_tiles, int wave,
-                  float scale_log2, int window, int* err) {
+                  float scale_log2, int window, int* err, const float* __restrict__ sinks, int planes) {
     constexpr int CB = D / 64;                    // blocks of 64 columns in a row of Q, K or V
     constexpr int Q_BLOCK = TA_BM * 128;          // bytes of one [128][64] block of Q
     constexpr int KV_BLOCK = QF_PAGE * 128;       // bytes of one [64][64] block of a page's keys or values
@@ -131,9 +131,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (leader) atomicOr(err, QF_ERR_NO_PAGE);
                     page = 0;
                 }
-                // row of the cache seen as one matrix [pages * 2 * kv_heads * 64][D]
-                const long long k_row = ((long long)page * 2 * site.kv_heads + kvh) * QF_PAGE;
-                const long long v_row = k_row + (long long)site.kv_heads * QF_PAGE;
+                // row of the cache seen as one matrix [pages * planes * kv_heads * 64][D]; with one plane per page the values
+                // are the keys themselves (the same rows fetched into the values' stage)
+                const long long k_row = ((long long)page * planes * site.kv_heads + kvh) * QF_PAGE;
+                const long long v_row = planes == 2 ? k_row + (long long)site.kv_heads * QF_PAGE : k_row;
                 if (leader) {
                     mbar_expect_tx(&bar_kv[stage], 2 * KV_BYTES);
 #pragma unroll
@@ -306,7 +307,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         if (!timed_out && n_tiles > 0 && !wait_all(&bar_pv, (n_tiles - 1) & 1)) timed_out = true;
         tc_fence_after();
         if (!SPLIT && !timed_out) {  // the loads are collective: every lane of the warp takes part, rows beyond the span store nothing
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            float den = l_run, keep = 1.f;
+            if (sinks) {  // a sink's term joins the sum of weights once, in base-2 units like the scores, on a common maximum
+                const float s2 = sinks[head] * 1.4426950408889634f, m_new = fmaxf(m_ref, s2);
+                keep = exp2f(m_ref - m_new);
+                den = l_run * keep + exp2f(s2 - m_new);
+            }
+            const float inv = den > 0.f ? keep / den : 0.f;
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t raw[32];
@@ -349,8 +356,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float m_other = theirs[D * TA_BM], l_other = theirs[(D + 1) * TA_BM];
             const float m_all = fmaxf(m_ref, m_other);
             const float f_mine = fast_exp2(m_ref - m_all), f_theirs = fast_exp2(m_other - m_all);
-            const float l_all = l_run * f_mine + l_other * f_theirs;
-            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+            float l_all = l_run * f_mine + l_other * f_theirs, keep = 1.f;
+            if (sinks) {
+                const float s2 = sinks[head] * 1.4426950408889634f, m_new = fmaxf(m_all, s2);
+                keep = exp2f(m_all - m_new);
+                l_all = l_all * keep + exp2f(s2 - m_new);
+            }
+            const float inv = l_all > 0.f ? keep / l_all : 0.f;
             const bool have = n_tiles > 0 && !timed_out;
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -380,7 +392,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 template <int D, bool SPLIT>
 static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, void* out, const int* cu_q, const int* tok_pos,
                           const int* slots, KvSite<bf16> site, int n_heads, int n_seqs, int max_q_len, float scale, int window,
-                          int* err, cudaStream_t stream) {
+                          int* err, const float* sinks, int planes, cudaStream_t stream) {
     size_t smem = (size_t)(D / 64) * TA_BM * 128 + 4 * (size_t)(D / 64) * QF_PAGE * 128 + TA_BM * 128 + 1024;
     auto kernel = prefill_tc_kernel<D, SPLIT>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -403,15 +415,18 @@ static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, v
     config.attrs = attr;
     config.numAttrs = SPLIT ? 2 : 1;
     return (int)cudaLaunchKernelEx(&config, kernel, q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs,
-                                   row_tiles, SPLIT ? qf_sm_count() / 2 : qf_sm_count(), scale * 1.4426950408889634f, window, err);
+                                   row_tiles, SPLIT ? qf_sm_count() / 2 : qf_sm_count(), scale * 1.4426950408889634f, window, err,
+                                   sinks, planes);
 }
 
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
-    // the cache pages must be what the map takes them for: [2][kv_heads][64][D] without gaps
-    if (page_elems != 2ll * kv_heads * QF_PAGE * D) return (int)cudaErrorInvalidValue;
+                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, const float* sinks,
+                  int shared_values, cudaStream_t stream) {
+    // the cache pages must be what the map takes them for: [planes][kv_heads][64][D] without gaps
+    const int planes = shared_values ? 1 : 2;
+    if (page_elems != (long long)planes * kv_heads * QF_PAGE * D) return (int)cudaErrorInvalidValue;
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     CUtensorMap q_map = {}, kv_map = {};
     const long long q_width = (long long)n_heads * D;
@@ -429,24 +444,35 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     const int span = window > 0 && window + TA_BM < max_kv_len ? window + TA_BM : max_kv_len;
     const long long room = (long long)qf_sm_count() * (D <= 64 ? 3 : 2);
     const bool split = D <= 64 ? span >= 16 * QF_PAGE && blocks <= room : span >= 32 * QF_PAGE && blocks * 2 <= room;
-    return split ? launch_variant<D, true>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
-                 : launch_variant<D, false>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
+    return split ? launch_variant<D, true>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, planes, stream)
+                 : launch_variant<D, false>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, planes, stream);
 }
 
 // The arguments of qf_attention_prefill (with `max_kv_len`, the bound that steers the sharing of a tile) and the number
 // of rows of q (n_tokens). cudaErrorInvalidValue for a head
 // size other than 64 or 128, or for cache pages with gaps (the caller then uses another kernel).
-QF_EXPORT int qf_attention_prefill_tc(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
-                                      void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
-                                      float scale, int window, int* err, cudaStream_t stream) {
+// `sinks` (float32 per query head, or null) and `shared_values` (pages of one plane whose rows are keys and values both) as
+// in the other attention kernels.
+QF_EXPORT int qf_attention_prefill_tc_ex(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                         void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                         int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                         float scale, int window, int* err, const float* sinks, int shared_values,
+                                         cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     if (head_dim == 64)
         return launch<64>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads, n_seqs,
-                          n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
+                          n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, stream);
     if (head_dim == 128)
         return launch<128>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads, n_seqs,
-                           n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
+                           n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, stream);
     return (int)cudaErrorInvalidValue;
+}
+
+QF_EXPORT int qf_attention_prefill_tc(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                      void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                      float scale, int window, int* err, cudaStream_t stream) {
+    return qf_attention_prefill_tc_ex(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                                      n_heads, n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, nullptr, 0, stream);
 }

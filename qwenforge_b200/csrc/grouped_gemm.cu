@@ -32,6 +32,7 @@ struct GroupedArgs {
     const int* n_tiles;
     int max_tiles;
     const int* a_rows;       // null: row r of A is row r
+    const float* row_scale;  // gated tiles: a factor per row on both halves before the gate (null: 1)
 };
 
 // Which group and which rows this block has; false if it has none.
@@ -110,8 +111,12 @@ grouped_gemm_plain_kernel(GroupedArgs g) {
 
 // bfloat16 on the tensor cores: a block of four warps makes a tile of 64 x 64, warp (wy, wx) its 32 x 32 quarter as
 // 2 x 4 tiles of m16n8k16; both operands arrive in slabs of 32 columns of K by 16-byte asynchronous copies, one slab ahead.
+// GATED: W_g = [gate rows | up rows] (n of each) and the tile's 64 weight rows are 32 gate rows and the 32 matching up rows;
+// a thread then holds a gate sum and the up sum of the same column, and the block writes 32 columns of
+// silu(s g) * (s u), s the row's scale: the gate/up product of an expert and its gate in one kernel.
 #define GT_BK 32
 #define GT_LD (GT_BK + 8)
+template <bool GATED>
 __global__ void __launch_bounds__(128)
 grouped_gemm_mma_kernel(GroupedArgs g) {
     grid_chain_entry();
@@ -122,7 +127,7 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
     const bf16* A = (const bf16*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
     const bf16* W = (const bf16*)g.w + (long long)group * g.w_group_stride;
     bf16* C = (bf16*)g.c + (g.tile_group ? 0 : (long long)group * g.c_group_cols);
-    const int n0 = blockIdx.x * GG_BN, N = g.n, K = g.k;
+    const int n0 = blockIdx.x * (GATED ? GG_BN / 2 : GG_BN), N = g.n, K = g.k;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wy = warp >> 1, wx = warp & 1;
     long long a_row[2];   // the two rows of A this thread fetches, through the row map if there is one
 #pragma unroll
@@ -138,9 +143,12 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
             const int idx = threadIdx.x + i * 128;
             const int r = idx >> 2, c = (idx & 3) * 8;
             const bool k_ok = k0 + c < K;
-            const bool a_ok = k_ok && a_row[i] >= 0, w_ok = k_ok && n0 + r < N;
+            // weight row of tile row r: GATED, rows 0..31 are gate rows n0.., rows 32..63 the up rows of the same columns
+            const int col = GATED ? n0 + (r & 31) : n0 + r;
+            const long long w_row = GATED ? (r < 32 ? col : (long long)N + col) : col;
+            const bool a_ok = k_ok && a_row[i] >= 0, w_ok = k_ok && col < N;
             cp_async_16(&a_s[buf][r][c], a_ok ? A + a_row[i] * g.lda + k0 + c : A, a_ok);
-            cp_async_16(&w_s[buf][r][c], w_ok ? W + (long long)(n0 + r) * g.ldw + k0 + c : W, w_ok);
+            cp_async_16(&w_s[buf][r][c], w_ok ? W + w_row * g.ldw + k0 + c : W, w_ok);
         }
     };
     float acc[2][4][4];
@@ -164,7 +172,9 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
 #pragma unroll
             for (int j2 = 0; j2 < 2; ++j2) {  // 16 weight rows per ldmatrix.x4
                 uint32_t wf[4];
-                ldmatrix_x4(wf, &w_s[buf][32 * wx + 16 * j2 + (lane >> 4) * 8 + (lane & 7)][16 * ks + ((lane >> 3) & 1) * 8]);
+                // GATED: warp wx has 16 columns: their gate rows (j2 = 0) and their up rows (j2 = 1)
+                const int w_base = GATED ? 32 * j2 + 16 * wx : 32 * wx + 16 * j2;
+                ldmatrix_x4(wf, &w_s[buf][w_base + (lane >> 4) * 8 + (lane & 7)][16 * ks + ((lane >> 3) & 1) * 8]);
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     mma_bf16_16816(acc[i][2 * j2], af[i], wf[0], wf[1]);
@@ -175,6 +185,30 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
         __syncthreads();
     }
     cp_async_wait<0>();
+    if (GATED) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int gm = m0 + 32 * wy + 16 * i + (lane >> 2) + 8 * half;
+                if (gm >= m_end) continue;
+                const float s = g.row_scale ? g.row_scale[gm] : 1.f;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int gn = n0 + 16 * wx + 8 * j + 2 * (lane & 3);
+                    const float g0 = s * acc[i][j][2 * half], g1 = s * acc[i][j][2 * half + 1];
+                    const float v0 = g0 / (1.0f + expf(-g0)) * (s * acc[i][2 + j][2 * half]);
+                    const float v1 = g1 / (1.0f + expf(-g1)) * (s * acc[i][2 + j][2 * half + 1]);
+                    bf16* dst = C + (long long)gm * g.ldc + gn;
+                    if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
+                    else {
+                        if (gn < N) dst[0] = __float2bfloat16_rn(v0);
+                        if (gn + 1 < N) dst[1] = __float2bfloat16_rn(v1);
+                    }
+                }
+            }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -300,10 +334,16 @@ QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long lo
                               long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
                               int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
                               const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
-                              cudaStream_t stream) {
+                              int gated, const float* row_scale, cudaStream_t stream) {
     if (rows <= 0 || n <= 0 || n_groups <= 0) return 0;
     GroupedArgs g{a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
-                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows};
+                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows, row_scale};
+    if (gated) {  // n = columns of the result (half of a group's weight rows); the small tensor-core tile only
+        if (!is_bf16 || !mma_takes(g) || (tile_group && tile_rows != QF_GROUP_BM)) return (int)cudaErrorInvalidValue;
+        const dim3 grid((n + GG_BN / 2 - 1) / (GG_BN / 2), tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
+        if (grid.y == 0 || grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+        return (int)launch_pdl(grouped_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, g);
+    }
     const bool large = tile_group ? tile_rows == GL_BM : (is_bf16 && mma_takes(g) && rows >= GL_MIN_ROWS);
     if (tile_group && tile_rows != GL_BM && tile_rows != QF_GROUP_BM) return (int)cudaErrorInvalidValue;
     if (large) {
@@ -317,7 +357,7 @@ QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long lo
     }
     const dim3 grid((n + GG_BN - 1) / GG_BN, tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
     if (grid.y == 0 || grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    if (is_bf16 && mma_takes(g)) return (int)launch_pdl(grouped_gemm_mma_kernel, grid, dim3(128), 0, stream, g);
+    if (is_bf16 && mma_takes(g)) return (int)launch_pdl(grouped_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, g);
     if (is_bf16) return (int)launch_pdl(grouped_gemm_plain_kernel<bf16>, grid, dim3(256), 0, stream, g);
     return (int)launch_pdl(grouped_gemm_plain_kernel<float>, grid, dim3(256), 0, stream, g);
 }
@@ -325,6 +365,6 @@ QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long lo
 // Whether a ragged product of these operands may use tiles of 128 rows (the plan has to be cut accordingly).
 QF_EXPORT int qf_grouped_gemm_large_takes(int is_bf16, const void* a, long long lda, const void* w, long long w_group_stride,
                                           long long ldw, int k) {
-    GroupedArgs g{a, lda, 0, w, w_group_stride, ldw, nullptr, 0, 0, 0, 0, k, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr};
+    GroupedArgs g{a, lda, 0, w, w_group_stride, ldw, nullptr, 0, 0, 0, 0, k, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr};
     return is_bf16 && mma_takes(g) ? 1 : 0;
 }

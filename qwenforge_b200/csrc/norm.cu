@@ -177,25 +177,38 @@ QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, lon
 //   hidden += y * rsqrt(mean(y^2) + eps_post) * post_weight;   out = hidden * rsqrt(mean(hidden^2) + eps_next) * next_weight
 // (the second half only when next_weight is given). Both sums of squares, both roots and the addition are float32. A block
 // per row; a thread keeps up to SW_KEEP of the row's elements in registers between the passes, wider rows are read again.
+// With `dest`, row t of y is not stored anywhere: it is the sum of `top` rows y[dest[t * top + k]] (each times
+// row_weight[that row], if given), summed in float32 in the order of k: what a mixture of experts leaves per token.
 #define SW_KEEP 16
 template <typename T>
 __global__ void __launch_bounds__(256)
 sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
-                     const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int width) {
+                     const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int width,
+                     const int* __restrict__ dest, int top, const float* __restrict__ row_weight) {
     grid_chain_entry();
     __shared__ float scratch[33];
     float* h = hidden + (size_t)blockIdx.x * width;
     const T* yr = y + (size_t)blockIdx.x * width;
+    auto y_at = [&](int c) -> float {
+        if (!dest) return Num<T>::to_f(yr[c]);
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = dest[(size_t)blockIdx.x * top + k];
+            const float v = Num<T>::to_f(y[(size_t)row * width + c]);
+            sum += row_weight ? v * row_weight[row] : v;
+        }
+        return sum;
+    };
     float kept[SW_KEEP];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < SW_KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
-        kept[u] = c < width ? Num<T>::to_f(yr[c]) : 0.f;
+        kept[u] = c < width ? y_at(c) : 0.f;
         ss += kept[u] * kept[u];
     }
     for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
-        const float v = Num<T>::to_f(yr[c]);
+        const float v = y_at(c);
         ss += v * v;
     }
     const float inv_y = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_post);
@@ -210,7 +223,7 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
         }
     }
     for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
-        const float v = h[c] + Num<T>::to_f(yr[c]) * inv_y * Num<T>::to_f(post_weight[c]);
+        const float v = h[c] + y_at(c) * inv_y * Num<T>::to_f(post_weight[c]);
         h[c] = v;
         ss += v * v;
     }
@@ -228,15 +241,19 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
 
 template <typename T>
 static int sandwich_launch(float* hidden, const void* y, const void* post_weight, float eps_post, const void* next_weight,
-                           float eps_next, void* out, int rows, int width, cudaStream_t stream) {
+                           float eps_next, void* out, int rows, int width, const int* dest, int top, const float* row_weight,
+                           cudaStream_t stream) {
     if (rows <= 0) return 0;
     return (int)launch_pdl(sandwich_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y, (const T*)post_weight,
-                           eps_post, (const T*)next_weight, eps_next, (T*)out, width);
+                           eps_post, (const T*)next_weight, eps_next, (T*)out, width, dest, top, row_weight);
 }
 
-// y, post_weight, next_weight (may be null) and out (null with it) share a dtype; hidden is float32 [rows, width].
+// y, post_weight, next_weight (may be null) and out (null with it) share a dtype; hidden is float32 [rows, width]. dest
+// (int32 [rows * top], or null), top and row_weight (float32 per row of y, or null): see above; y then has as many rows
+// as dest names.
 QF_EXPORT int qf_sandwich_norm(int is_bf16, float* hidden, const void* y, const void* post_weight, float eps_post,
-                               const void* next_weight, float eps_next, void* out, int rows, int width, cudaStream_t stream) {
-    return is_bf16 ? sandwich_launch<bf16>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, stream)
-                   : sandwich_launch<float>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, stream);
+                               const void* next_weight, float eps_next, void* out, int rows, int width, const int* dest, int top,
+                               const float* row_weight, cudaStream_t stream) {
+    return is_bf16 ? sandwich_launch<bf16>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream)
+                   : sandwich_launch<float>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream);
 }

@@ -30,7 +30,7 @@ from pathlib import Path
 
 import torch
 
-from ..cache import PAGE_TOKENS, round_up
+from ..cache import PAGE_TOKENS, CacheFull, round_up
 from .model import Model
 
 
@@ -49,8 +49,12 @@ def parse_args(argv=None):
     return p.parse_args(argv)
 
 
-def replay(model: Model, cache, lines, out_dir: Path, report=print, dump_dir: Path | None = None) -> None:
+def replay(model: Model, cache, lines, out_dir: Path, report=print, dump_dir: Path | None = None,
+           max_tokens: int | None = None) -> None:
+    """`max_tokens`: the most tokens that live requests may hold together (the caller's promise, which sized the cache); a
+    step that would exceed it is refused before it runs."""
     slots: dict[str, int] = {}
+    held: dict[str, int] = {}
     current = {"step": None}
     if dump_dir is not None:
         def observe(index, hidden, delta):
@@ -70,6 +74,9 @@ def replay(model: Model, cache, lines, out_dir: Path, report=print, dump_dir: Pa
                 slots[key] = cache.open()
             entries.append((slots[key], [int(t) for t in item["tokens"]]))
             want.append([int(w) for w in item.get("want", [])])
+            held[key] = held.get(key, 0) + len(item["tokens"])
+        if max_tokens is not None and sum(held.values()) > max_tokens:
+            raise CacheFull(f"step {step}: live requests would hold {sum(held.values())} tokens, --max-tokens is {max_tokens}")
         if entries:
             logits = model.step(cache, entries, want)
             if logits is not None:
@@ -78,6 +85,7 @@ def replay(model: Model, cache, lines, out_dir: Path, report=print, dump_dir: Pa
             model.raise_on_kernel_error()
         for key in record.get("end", []):
             key = str(key)
+            held.pop(key, None)
             if key in slots:
                 cache.close(slots.pop(key))
         report(f"done {step}")
@@ -97,7 +105,8 @@ def main(argv=None) -> int:
         dump_dir = Path(args.dump_layers) if args.dump_layers else None
         if dump_dir is not None:
             dump_dir.mkdir(parents=True, exist_ok=True)
-        replay(model, cache, sys.stdin, out_dir, report=lambda text: print(text, flush=True), dump_dir=dump_dir)
+        replay(model, cache, sys.stdin, out_dir, report=lambda text: print(text, flush=True), dump_dir=dump_dir,
+               max_tokens=args.max_tokens)
     return 0
 
 

@@ -2,14 +2,14 @@ from .kernels import (TC_PLAIN, TC_SWIGLU, tc_gemm, tc_gemm_takes, tc_gemm_is_pe
                       skinny_gemm_takes, skinny_gemm_pays, decode_advance, decode_advance_embed, FAST_ATTENTION_HEAD_DIMS, GENERIC_DECODE_CHUNK, DecodeScratch, attention_decode, attention_decode_plan, attention_decode_warps, fold_project, fold_project_pays, fold_project_takes, attention_prefill, attention_prefill_tc, TC_ATTENTION_HEAD_DIMS, ERR_NO_PAGE, ERR_ROW_RANGE, ERR_TOKEN_RANGE, KernelError, KvSiteArgs, add_rms_norm,
                       attention_generic, describe_error_word, embed_gather, gather_rows, gather_rows_norm, gemm_f32, require_cuda,
                       rope_cache_write, sample, sm_count, swiglu, embed_positions, sandwich_norm, clamped_glu,
-                      latent_norm_cache, head_linear, MoePlan, moe_plan, moe_gather, moe_combine, expert_linear, scaled_swiglu, tc_gemm_grouped, tc_gemm_grouped_takes, moe_tile_rows, MOE_FUSED_ROUTER_MAX,
+                      latent_norm_cache, head_linear, MoePlan, moe_plan, moe_gather, moe_combine, expert_linear, scaled_swiglu, tc_gemm_grouped, tc_gemm_grouped_takes, expert_gate_up, expert_gate_takes, moe_tile_rows, MOE_FUSED_ROUTER_MAX,
                       ERR_POSITION_RANGE, GENERIC_MAX_HEAD_DIM)
 from .linear import linear, linear_rows, own_tensor_core_products, use_own_tensor_core_products
 
 __all__ = [
     "embed_positions", "sandwich_norm", "clamped_glu", "latent_norm_cache", "head_linear", "MoePlan", "moe_plan", "moe_gather",
     "moe_combine", "expert_linear", "ERR_POSITION_RANGE", "GENERIC_MAX_HEAD_DIM", "scaled_swiglu", "moe_tile_rows",
-    "MOE_FUSED_ROUTER_MAX", "linear_rows", "tc_gemm_grouped", "tc_gemm_grouped_takes",
+    "MOE_FUSED_ROUTER_MAX", "linear_rows", "tc_gemm_grouped", "tc_gemm_grouped_takes", "expert_gate_up", "expert_gate_takes",
     "ERR_NO_PAGE", "ERR_ROW_RANGE", "ERR_TOKEN_RANGE", "KernelError", "KvSiteArgs", "add_rms_norm",
     "attention_generic", "describe_error_word", "embed_gather", "gather_rows", "gather_rows_norm", "gemm_f32", "rope_cache_write",
     "sample", "swiglu", "linear", "own_tensor_core_products", "use_own_tensor_core_products", "require_cuda", "FAST_ATTENTION_HEAD_DIMS", "GENERIC_DECODE_CHUNK", "DecodeScratch",

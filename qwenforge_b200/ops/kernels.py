@@ -310,7 +310,8 @@ TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                          slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
-                         window: int, err: torch.Tensor, max_kv_len: Optional[int] = None) -> None:
+                         window: int, err: torch.Tensor, max_kv_len: Optional[int] = None,
+                         sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
     """The same attention on the fifth-generation tensor cores (tcgen05, accumulators in tensor memory): blocks of
     128 query rows; bfloat16, head sizes 64 and 128, cache pages without gaps. `max_kv_len` as in `attention_prefill`:
     with few tiles of many pages, two blocks of a cluster share a tile."""
@@ -323,13 +324,17 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
                           "use attention_prefill")
     if q.shape[1] != n_heads * d or out.shape != q.shape:
         raise KernelError("attention_prefill_tc: q/out widths do not match the head count")
-    if site.page_elems != 2 * site.kv_heads * site.storage.shape[-2] * d:
+    if site.page_elems != (1 if shared_values else 2) * site.kv_heads * site.storage.shape[-2] * d:
         raise KernelError("attention_prefill_tc: the cache pages have gaps; use attention_prefill")
-    _check(library("attention_prefill_tc").qf_attention_prefill_tc(
+    if sinks is not None:
+        _dev("sinks", sinks, torch.float32)
+        if sinks.numel() != n_heads:
+            raise KernelError("attention_prefill_tc: sinks must hold one float32 per query head")
+    _check(library("attention_prefill_tc").qf_attention_prefill_tc_ex(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
-        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()),
-        "attention_prefill_tc")
+        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err),
+        _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_prefill_tc")
 
 
 class DecodeScratch:
@@ -989,16 +994,29 @@ def embed_positions(ids: torch.Tensor, tok_pos: torch.Tensor, table: torch.Tenso
 
 def sandwich_norm(hidden: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
                   next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
-                  out: Optional[torch.Tensor] = None) -> None:
+                  out: Optional[torch.Tensor] = None, dest: Optional[torch.Tensor] = None, top: int = 1,
+                  row_weight: Optional[torch.Tensor] = None) -> None:
     """hidden += rmsnorm(y) * post_weight; then, if `next_weight` is given, out = rmsnorm(hidden) * next_weight: a
     sublayer's output normalised on its way into the float32 stream, and the stream normalised for the next sublayer, in
-    one pass. y, the weights and out share a dtype."""
+    one pass. y, the weights and out share a dtype. With `dest` (int32 [rows * top]), row t of the sublayer's output is the
+    sum of the `top` rows y[dest[t * top + k]] (times row_weight[that row], float32, if given), summed in float32 on the way
+    in: what a mixture of experts leaves per token (`MoePlan.dest`)."""
     _dev("hidden", hidden, torch.float32)
     _dev("y", y)
     _dev("post_weight", post_weight, y.dtype)
     rows, width = hidden.shape
-    if y.shape != hidden.shape or post_weight.numel() != width:
-        raise KernelError("sandwich_norm: y must have the stream's shape and post_weight its width")
+    if dest is not None:
+        _dev("dest", dest, torch.int32)
+        if dest.numel() != rows * top or y.dim() != 2 or y.shape[1] != width:
+            raise KernelError("sandwich_norm: dest must name `top` rows of y [*, width] per row of the stream")
+        if row_weight is not None:
+            _dev("row_weight", row_weight, torch.float32)
+            if row_weight.numel() != y.shape[0]:
+                raise KernelError("sandwich_norm: row_weight must hold one float32 per row of y")
+    elif y.shape != hidden.shape:
+        raise KernelError("sandwich_norm: y must have the stream's shape")
+    if post_weight.numel() != width:
+        raise KernelError("sandwich_norm: post_weight must have the stream's width")
     if next_weight is not None:
         _dev("next_weight", next_weight, y.dtype)
         _dev("out", out, y.dtype)
@@ -1006,7 +1024,8 @@ def sandwich_norm(hidden: torch.Tensor, y: torch.Tensor, post_weight: torch.Tens
             raise KernelError("sandwich_norm: out must have the stream's shape and next_weight its width")
     _check(library("norm").qf_sandwich_norm(_I(_is_bf16(y.dtype)), _ptr(hidden), _ptr(y), _ptr(post_weight), _F(post_eps),
                                             _ptr(next_weight), _F(next_eps), _ptr(out if next_weight is not None else None),
-                                            _I(rows), _I(width), _stream()), "sandwich_norm")
+                                            _I(rows), _I(width), _ptr(dest), _I(top if dest is not None else 1),
+                                            _ptr(row_weight if dest is not None else None), _stream()), "sandwich_norm")
 
 
 def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, out: torch.Tensor) -> None:
@@ -1052,14 +1071,16 @@ def latent_norm_cache(down: torch.Tensor, q_rank: int, q_norm: Optional[torch.Te
         _I(1 if write_cache else 0), _I(n), _ptr(err), _stream()), "latent_norm_cache")
 
 
-def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None) -> None:
+def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None, gated=False, row_scale=None) -> None:
     groups, n, k = weight.shape
+    if gated:
+        n //= 2   # columns of the result
     code = library("grouped_gemm").qf_grouped_gemm(
         _I(_is_bf16(x.dtype)), _ptr(x), _LL(x.stride(0)), _LL(a_group_cols), _ptr(weight), _LL(weight.stride(0)),
         _LL(weight.stride(1)), _ptr(out), _LL(out.stride(0)), _LL(c_group_cols), _I(rows), _I(n), _I(k), _I(groups),
         _ptr(plan.tile_group if plan else None), _ptr(plan.tile_row0 if plan else None), _ptr(plan.offsets if plan else None),
         _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _I(plan.tile_rows if plan else 0),
-        _ptr(a_rows), _stream())
+        _ptr(a_rows), _I(int(gated)), _ptr(row_scale), _stream())
     if code == 1:
         raise KernelError("grouped_gemm: the plan's tiles do not fit these operands (tiles of 128 rows need bfloat16 operands "
                           "whose K and strides are multiples of 8), or the grid is too large")
@@ -1179,6 +1200,32 @@ def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: tor
     if groups != plan.n_experts or x.shape != ((plan.n_tokens if gather else plan.pairs), k) or out.shape != (plan.pairs, n):
         raise KernelError(f"expert_linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
     _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None)
+
+
+def expert_gate_takes(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan) -> bool:
+    """Whether `expert_gate_up` takes these operands: bfloat16, tiles of 64 rows, K and the strides multiples of 8, 16-byte
+    aligned bases."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and plan.tile_rows == GROUP_TILE_ROWS and weight.shape[1] % 2 == 0
+            and all(v % 8 == 0 for v in (x.stride(0), weight.stride(0), weight.stride(1), weight.shape[2]))
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def expert_gate_up(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor,
+                   row_scale: Optional[torch.Tensor] = None, gather: bool = False) -> None:
+    """An expert's gate/up product and its gate in one kernel: out[row] = silu(s g) * (s u) with [g | u] = x[row] @
+    weight[expert of the row].T, weight [E, 2 F, K] (gate rows then up rows), out [T * top, F], s = row_scale[row] (float32) or
+    1. `gather` as in `expert_linear`. bfloat16 on the tensor cores only (`expert_gate_takes`)."""
+    _dev("x", x, torch.bfloat16)
+    _dev("weight", weight, torch.bfloat16)
+    _dev("out", out, torch.bfloat16)
+    groups, n2, k = weight.shape
+    if not expert_gate_takes(x, weight, plan):
+        raise KernelError("expert_gate_up: bfloat16 operands with K and strides multiples of 8 and a plan of 64-row tiles")
+    if groups != plan.n_experts or x.shape != ((plan.n_tokens if gather else plan.pairs), k) or out.shape != (plan.pairs, n2 // 2):
+        raise KernelError(f"expert_gate_up: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
+    if row_scale is not None:
+        _dev("row_scale", row_scale, torch.float32)
+    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None, True, row_scale)
 
 
 def scaled_swiglu(gate_up: torch.Tensor, row_scale: torch.Tensor, out: torch.Tensor) -> None:

@@ -97,19 +97,44 @@ class PendingNormed:
     """A sublayer's output that still has to be normalised (RMS, weight, eps) and added to the residual stream: what a
     block with norms after its sublayers hands to whoever runs next, so that the addition rides on that part's first norm
     kernel (`ops.sandwich_norm`). The model resolves it itself before anything that only knows plain deltas."""
-    __slots__ = ("y", "weight", "eps")
+    __slots__ = ("y", "weight", "eps", "rows")
 
-    def __init__(self, y: torch.Tensor, weight: torch.Tensor, eps: float):
-        self.y, self.weight, self.eps = y, weight, eps
+    def __init__(self, y, weight: torch.Tensor, eps: float):
+        """y: the sublayer's output [T, W], or a `RowSum` whose rows are still to be summed per token."""
+        self.rows = y if isinstance(y, RowSum) else None
+        self.y = y.rows if isinstance(y, RowSum) else y
+        self.weight, self.eps = weight, eps
+
+    def into(self, hidden: torch.Tensor, next_weight=None, next_eps: float = 0.0, out=None) -> None:
+        """hidden += norm(y); and, with `next_weight`, out = the next norm of the stream, in the same kernel."""
+        from .. import ops
+        r = self.rows
+        ops.sandwich_norm(hidden, self.y, self.weight, self.eps, next_weight, next_eps, out,
+                          dest=None if r is None else r.dest, top=1 if r is None else r.top,
+                          row_weight=None if r is None else r.row_weight)
 
     def add_to(self, hidden: torch.Tensor) -> None:
-        from .. import ops
-        ops.sandwich_norm(hidden, self.y, self.weight, self.eps)
+        self.into(hidden)
 
     def value(self) -> torch.Tensor:
         """The float32 tensor that will be added (for diagnosis; not on the product path)."""
         y = self.y.to(torch.float32)
+        if self.rows is not None:
+            r = self.rows
+            if r.row_weight is not None:
+                y = y * r.row_weight[:, None]
+            y = y[r.dest.long()].view(-1, r.top, y.shape[1]).sum(1)
         return y * torch.rsqrt(y.square().mean(-1, keepdim=True) + self.eps) * self.weight.to(torch.float32)
+
+
+class RowSum:
+    """A sublayer's output that is not stored per token: token t's row is the sum of the `top` rows rows[dest[t * top + k]]
+    (each times row_weight[that row], if given). A feed-forward with routed experts hands this to a block that can take it
+    (`forward_rows`), so that the sum rides on the kernel that reads the output next."""
+    __slots__ = ("rows", "dest", "top", "row_weight")
+
+    def __init__(self, rows: torch.Tensor, dest: torch.Tensor, top: int, row_weight=None):
+        self.rows, self.dest, self.top, self.row_weight = rows, dest, top, row_weight
 
 
 class Embedding(Part):

@@ -7,7 +7,6 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
 from .base import Norm, Part, PendingNormed
 from .registry import build_part, register_part
 
@@ -78,7 +77,7 @@ class SandwichBlock(Part):
         weight, eps = self.mixer_norm.fused_rms()
         if isinstance(delta, PendingNormed):
             x = torch.empty(hidden.shape, dtype=weight.dtype, device=hidden.device)
-            ops.sandwich_norm(hidden, delta.y, delta.weight, delta.eps, weight, eps, x)
+            delta.into(hidden, weight, eps, x)
         else:
             x = self.mixer_norm.forward(hidden, delta)
         y = self.mixer.forward(x, ctx, site, writes_cache)
@@ -87,8 +86,10 @@ class SandwichBlock(Part):
             return post
         weight, eps = self.feed_forward_norm.fused_rms()
         x = torch.empty(hidden.shape, dtype=weight.dtype, device=hidden.device)
-        ops.sandwich_norm(hidden, post.y, post.weight, post.eps, weight, eps, x)
-        return PendingNormed(self.feed_forward.forward(x, ctx), *self.feed_forward_post_norm.fused_rms())
+        post.into(hidden, weight, eps, x)
+        # a feed-forward that leaves several rows per token hands them over unsummed: the next norm kernel adds them up
+        run = getattr(self.feed_forward, "forward_rows", None) or self.feed_forward.forward
+        return PendingNormed(run(x, ctx), *self.feed_forward_post_norm.fused_rms())
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -17,7 +17,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FeedForward, TensorSpec
+from .base import FeedForward, RowSum, TensorSpec
 from .registry import register_part
 
 
@@ -62,6 +62,13 @@ class RoutedExperts(FeedForward):
         return [self.router, self.gate_up, self.down]
 
     def forward(self, x, ctx):
+        out = torch.empty_like(x)
+        r = self.forward_rows(x, ctx)
+        ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None)
+        return out
+
+    def forward_rows(self, x, ctx) -> RowSum:
+        """The experts' output rows, `top` per token and not yet summed (see `RowSum`)."""
         # float32 logits from the rows as the experts see them (their bfloat16 rounding on the 16-bit path: products of
         # bfloat16 numbers are exact in float32, and the sums are float32)
         n = x.shape[0]
@@ -71,6 +78,7 @@ class RoutedExperts(FeedForward):
             plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router)   # few tokens: one launch
         else:
             plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows)
+        self._plan = plan
         # A weight on the expert's input moves behind its first product (G (w h) = w (G h), and the same for U), where it
         # meets float32 sums.
         on_input = self.weight_on == "input"
@@ -84,20 +92,19 @@ class RoutedExperts(FeedForward):
             ops.tc_gemm_grouped(ops.TC_SWIGLU, rows, self.gate_up, plan, act, plan.sorted_weight if on_input else None, ctx.err)
             y = torch.empty_like(rows)
             ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
-            out = torch.empty_like(x)
-            ops.moe_combine(y, plan, out, not on_input)
-            return out
+            return RowSum(y, plan.dest, self.top, None if on_input else plan.sorted_weight)
         # otherwise the sorted rows are read through the plan's row map and never stored
-        gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
-        ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
-        if on_input:
-            ops.scaled_swiglu(gate_up, plan.sorted_weight, act)
+        if ops.expert_gate_takes(x, self.gate_up, plan):   # the gate in the product's epilogue
+            ops.expert_gate_up(x, self.gate_up, plan, act, plan.sorted_weight if on_input else None, gather=True)
         else:
-            ops.swiglu(gate_up, act)
+            gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
+            ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
+            if on_input:
+                ops.scaled_swiglu(gate_up, plan.sorted_weight, act)
+            else:
+                ops.swiglu(gate_up, act)
         ops.expert_linear(act, self.down, plan, rows)
-        out = torch.empty_like(x)
-        ops.moe_combine(rows, plan, out, self.weight_on == "output")
-        return out
+        return RowSum(rows, plan.dest, self.top, None if on_input else plan.sorted_weight)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -22,6 +22,7 @@ import torch
 
 from .. import ops
 from ..cache import PAGE_TOKENS, KvNeed
+from .attention import TC_PREFILL_MIN_TOKENS
 from .base import Mixer, TensorSpec
 from .registry import register_part
 
@@ -68,6 +69,8 @@ class LatentAttention(Mixer):
             libs.add("gemm_f32")
         elif self.kv_rank in ops.FAST_ATTENTION_HEAD_DIMS:
             libs |= {"attention_decode", "attention_prefill", "skinny_gemm"}
+            if self.kv_rank in ops.TC_ATTENTION_HEAD_DIMS:
+                libs.add("attention_prefill_tc")
         return libs
 
     def cache_need(self):
@@ -120,7 +123,11 @@ class LatentAttention(Mixer):
                                  self.window, n_splits, ctx.decode_scratch, ctx.err, self.decode_plan(ctx, n_splits),
                                  sinks=self.sinks, shared_values=True)
         elif fast:
-            ops.attention_prefill(q_in_latent, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, h, ctx.n_seqs, ctx.max_q_len,
+            # long steps on the tcgen05 kernel (blocks of 128 query rows), from the same sizes as any attention's
+            least = TC_PREFILL_MIN_TOKENS.get(r)
+            prefill = (ops.attention_prefill_tc if least is not None and n >= least and ctx.max_q_len >= 128
+                       else ops.attention_prefill)
+            prefill(q_in_latent, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, h, ctx.n_seqs, ctx.max_q_len,
                                   self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len, sinks=self.sinks,
                                   shared_values=True)
         else:

@@ -171,7 +171,10 @@ def embed_positions(ids, tok_pos, table, positions, out, err):
     out.copy_((_f(table[ids.long()]) + _f(positions[tok_pos.long()])).to(torch.float32))
 
 
-def sandwich_norm(hidden, y, post_weight, post_eps, next_weight=None, next_eps=0.0, out=None):
+def sandwich_norm(hidden, y, post_weight, post_eps, next_weight=None, next_eps=0.0, out=None, dest=None, top=1, row_weight=None):
+    if dest is not None:
+        y = _f(y) if row_weight is None else _f(y) * _f(row_weight)[:, None]
+        y = y[dest.long()].view(-1, top, y.shape[1]).sum(1)
     hidden += _rms(y, post_weight, post_eps).to(torch.float32)
     if next_weight is not None:
         out.copy_(_rms(hidden, next_weight, next_eps).to(out.dtype))
@@ -218,6 +221,10 @@ def linear_rows(x, weight, out_dtype=None):
 
 def moe_tile_rows(n_tokens, n_experts, top, weight):
     return 64
+
+
+def expert_gate_takes(x, weight, plan):
+    return False
 
 
 def tc_gemm_grouped(epilogue, x, weight, plan, out, row_scale=None, err=None):
@@ -274,7 +281,7 @@ def expert_linear(x, weight, plan, out, gather=False):
     out.copy_(torch.einsum("rk,rnk->rn", rows, _f(weight)[plan.row_expert]).to(out.dtype))
 
 
-ALL = dict(linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
+ALL = dict(expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
            head_linear=head_linear, moe_plan=moe_plan, moe_gather=moe_gather, moe_combine=moe_combine, expert_linear=expert_linear,
            embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
            linear=linear, rope_cache_write=rope_cache_write, attention_generic=attention_generic, swiglu=swiglu,

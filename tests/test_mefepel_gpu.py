@@ -40,6 +40,9 @@ def logits_close(got, want, dtype, what="", margins=None):
     # (A row routed otherwise also moves the few later rows whose attention hangs on it, in the layers above: so even among
     # the clearly routed rows a few in a hundred may be far off, while the typical row is well within rounding.)
     assert bool(torch.isfinite(err).all())
+    if err.numel() < 30:     # too few rows for a statement about most of them
+        assert float(err.median()) <= 0.05, f"{what}: median {float(err.median()):.3e}"
+        return
     clear = err if margins is None else err[margins > 0.03]
     assert clear.numel() >= 0.6 * err.numel()
     far_off = float((clear > 0.15).double().mean())
@@ -85,6 +88,25 @@ def test_sandwich_norm(dtype, width):
     refs.sandwich_norm(only_add, y, w1, 1e-5)
     ops.sandwich_norm(hidden, y, w1, 1e-5)
     assert max_err(hidden, only_add) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_sandwich_norm_sums_a_tokens_rows_on_the_way_in(dtype, weighted):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    tokens, top, width = 9, 3, 200
+    hidden = torch.randn(tokens, width, generator=g).to(DEV)
+    rows = torch.randn(tokens * top, width, generator=g).to(dtype).to(DEV)
+    dest = torch.randperm(tokens * top, generator=g).int().to(DEV)
+    row_weight = torch.rand(tokens * top, generator=g).to(DEV) if weighted else None
+    w1, w2 = (1 + 0.2 * torch.randn(width, generator=g)).to(dtype).to(DEV), (1 + 0.2 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    want_h, want_out = hidden.clone(), torch.empty(tokens, width, dtype=dtype, device=DEV)
+    refs.sandwich_norm(want_h, rows, w1, 1e-5, w2, 1e-5, want_out, dest=dest, top=top, row_weight=row_weight)
+    out = torch.empty_like(want_out)
+    ops.sandwich_norm(hidden, rows, w1, 1e-5, w2, 1e-5, out, dest=dest, top=top, row_weight=row_weight)
+    assert max_err(hidden, want_h) < 2e-5
+    close(out, want_out, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -170,6 +192,13 @@ def test_routing_and_expert_products(dtype, shape):
     act = torch.empty(plan.pairs, ff, dtype=dtype, device=DEV)
     ops.swiglu(gate_up, act)
     close(act_scaled, act, torch.bfloat16, "the weight before and behind the product")
+    if ops.expert_gate_takes(x, w1, plan):   # bfloat16, tiles of 64 rows: the gate in the product's epilogue
+        fused = torch.full((plan.pairs, ff), 7.0, dtype=dtype, device=DEV)
+        ops.expert_gate_up(x, w1, plan, fused, plan.sorted_weight, gather=True)
+        gu = torch.einsum("rk,rnk->rn", x.double()[sorted_token.to(DEV)], w1.double()[row_expert.to(DEV)]) * plan.sorted_weight.double()[:, None]
+        close(fused, gu[:, :ff] * torch.sigmoid(gu[:, :ff]) * gu[:, ff:], dtype, "gate in the small tile's epilogue")
+    else:
+        assert dtype == torch.float32 or tile_rows == 128 or width % 8
     y = torch.empty(plan.pairs, width, dtype=dtype, device=DEV)
     ops.expert_linear(act, w2, plan, y)
     close(y, torch.einsum("rk,rnk->rn", act.double(), w2.double()[row_expert.to(DEV)]), dtype, "down of the experts")
@@ -298,6 +327,13 @@ def test_tensor_core_attention_with_sinks_over_a_shared_plane(rank, heads):
     ops.attention_prefill(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 3, max(new), scale, 0, err,
                           max_kv_len=max(lengths), sinks=sinks, shared_values=True)
     close(out, _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale), dtype, "prefill")
+    if rank in (64, 128):   # the tcgen05 kernel: blocks of 128 rows, also as pairs of blocks that share a tile
+        for lengths, new in (([700, 300, 129], [700, 130, 2]), ([1400], [1400])):
+            cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 16)
+            out = torch.empty_like(q)
+            ops.attention_prefill_tc(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, len(lengths), max(new), scale, 0,
+                                     err, max_kv_len=max(lengths), sinks=sinks, shared_values=True)
+            close(out, _latent_reference(latents, q, sinks, lengths, new, heads, rank, scale), dtype, f"tcgen05 prefill {new}")
     for n_splits in (1, 4):
         lengths, new = [1500, 64, 65, 1], [1, 1, 1, 1]
         cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 7 + n_splits)
@@ -309,12 +345,12 @@ def test_tensor_core_attention_with_sinks_over_a_shared_plane(rank, heads):
     assert int(err) == 0
 
 
-@pytest.mark.parametrize("kernel", ["generic", "prefill", "decode"])
+@pytest.mark.parametrize("kernel", ["generic", "prefill", "prefill_tc", "decode"])
 def test_a_large_sink_takes_the_weight_and_a_small_one_none(kernel):
     """With a sink far above every score the output vanishes; far below, the result is the plain softmax's."""
     from qwenforge_b200 import ops
     dtype, rank, heads, scale = torch.bfloat16, 64, 4, 0.1
-    lengths, new = ([300], [1]) if kernel == "decode" else ([300], [100])
+    lengths, new = ([300], [1]) if kernel == "decode" else ([300], [300]) if kernel == "prefill_tc" else ([300], [100])
     for sink_value, what in ((60.0, "large"), (-60.0, "small")):
         cache, site, args, latents, q, sinks, ctx = _latent_case(dtype, rank, heads, lengths, new, 9, sink_value)
         err = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -322,9 +358,9 @@ def test_a_large_sink_takes_the_weight_and_a_small_one_none(kernel):
         if kernel == "generic":
             ops.attention_generic(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, max(new), scale, 0, err,
                                   sinks=sinks, shared_values=True)
-        elif kernel == "prefill":
-            ops.attention_prefill(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, max(new), scale, 0, err,
-                                  sinks=sinks, shared_values=True)
+        elif kernel in ("prefill", "prefill_tc"):
+            run = ops.attention_prefill if kernel == "prefill" else ops.attention_prefill_tc
+            run(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, max(new), scale, 0, err, sinks=sinks, shared_values=True)
         else:
             ops.attention_decode(q, out, ctx["cu_q"], ctx["tok_pos"], ctx["slots"], args, heads, 1, scale, 0, 2,
                                  ops.DecodeScratch(torch.device(DEV)), err, sinks=sinks, shared_values=True)
