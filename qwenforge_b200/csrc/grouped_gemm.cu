@@ -110,18 +110,19 @@ grouped_gemm_plain_kernel(GroupedArgs g) {
 }
 
 // bfloat16 on the tensor cores: a block of four warps makes a tile of 64 x 64, warp (wy, wx) its 32 x 32 quarter as
-// 2 x 4 tiles of m16n8k16; both operands arrive in slabs of 32 columns of K by 16-byte asynchronous copies, one slab ahead.
+// 2 x 4 tiles of m16n8k16; both operands arrive in slabs of 32 columns of K by 16-byte asynchronous copies, three slabs ahead.
 // GATED: W_g = [gate rows | up rows] (n of each) and the tile's 64 weight rows are 32 gate rows and the 32 matching up rows;
 // a thread then holds a gate sum and the up sum of the same column, and the block writes 32 columns of
 // silu(s g) * (s u), s the row's scale: the gate/up product of an expert and its gate in one kernel.
 #define GT_BK 32
 #define GT_LD (GT_BK + 8)
+#define GT_STAGES 4
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 grouped_gemm_mma_kernel(GroupedArgs g) {
     grid_chain_entry();
-    __shared__ __align__(16) bf16 a_s[2][QF_GROUP_BM][GT_LD];
-    __shared__ __align__(16) bf16 w_s[2][GG_BN][GT_LD];
+    __shared__ __align__(16) bf16 a_s[GT_STAGES][QF_GROUP_BM][GT_LD];
+    __shared__ __align__(16) bf16 w_s[GT_STAGES][GG_BN][GT_LD];
     int group, m0, m_end;
     if (!grouped_tile<QF_GROUP_BM>(g, group, m0, m_end)) return;
     const bf16* A = (const bf16*)g.a + (g.tile_group ? 0 : (long long)group * g.a_group_cols);
@@ -156,14 +157,19 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
     for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
-    fetch(0, 0);
-    cp_async_commit();
-    for (int k0 = 0, turn = 0; k0 < K; k0 += GT_BK, ++turn) {
-        const int buf = turn & 1;
-        if (k0 + GT_BK < K) fetch(k0 + GT_BK, buf ^ 1);
+    // A step of a few rows has a handful of blocks that each walk all of K: what bounds them is the chain of fetches, so
+    // three slabs are on their way while one is multiplied.
+    const int n_slabs = (K + GT_BK - 1) / GT_BK;
+    for (int s = 0; s < GT_STAGES - 1; ++s) {
+        if (s < n_slabs) fetch(s * GT_BK, s);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+    }
+    for (int slab = 0; slab < n_slabs; ++slab) {
+        cp_async_wait<GT_STAGES - 2>();
+        __syncthreads();   // slab `slab` has arrived for everyone, and everyone is done with the buffer fetched next
+        if (slab + GT_STAGES - 1 < n_slabs) fetch((slab + GT_STAGES - 1) * GT_BK, (slab + GT_STAGES - 1) % GT_STAGES);
+        cp_async_commit();
+        const int buf = slab % GT_STAGES;
 #pragma unroll
         for (int ks = 0; ks < GT_BK / 16; ++ks) {
             uint32_t af[2][4];
@@ -182,7 +188,6 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
                 }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
     if (GATED) {

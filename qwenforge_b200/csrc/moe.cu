@@ -25,18 +25,18 @@
 // and in row order sorted_token [pairs], sorted_weight float32 [pairs]; offsets [experts + 1]; tile_group, tile_row0
 // [max_tiles]; n_tiles [1].
 __global__ void __launch_bounds__(MOE_PLAN_THREADS)
-moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                 int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ sorted_token,
                 float* __restrict__ sorted_weight, int* __restrict__ dest, int* __restrict__ offsets,
                 int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles,
-                int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16,
-                float* __restrict__ logits_out) {
+                int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;                   // [experts]: rows per expert, then every expert's first row
     int* first_tile = shared + n_experts;   // [experts + 1]
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
-    if (x) {  // the router's product first: logits_out[t][e] = sum_c x[t][c] * router[e][c], a warp per logit
+    if (x) {  // the router's product first: z[t][e] = sum_c x[t][c] * router[e][c], a warp per logit, kept in shared memory
+        float* logits_out = reinterpret_cast<float*>(shared + 2 * n_experts + 1);
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
         for (int i = warp; i < n_tokens * n_experts; i += n_warps) {
             const int t = i / n_experts, e = i % n_experts;
@@ -54,7 +54,6 @@ moe_plan_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, i
             if (lane == 0) logits_out[i] = sum;
         }
         logits = logits_out;
-        __threadfence_block();
     }
     __syncthreads();
     // pass 1: choose, and take a rank among the expert's rows
@@ -158,20 +157,19 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
 
 // pairs = n_tokens * top: pair_expert, pair_weight (scratch), sorted_token, sorted_weight and dest have that many elements;
 // tile_group and tile_row0 max_tiles >= ceil(pairs / tile_rows) + n_experts. Either `logits` float32 [n_tokens][n_experts]
-// is given, or x [n_tokens][width] and router [n_experts][width] (both bfloat16 or both float32) with logits_out as scratch
-// for the logits the kernel then makes itself.
+// is given, or x [n_tokens][width] and router [n_experts][width] (both bfloat16 or both float32), from which the kernel makes
+// the logits itself in shared memory (n_tokens * n_experts <= 8192).
 QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                           int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
                           int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
-                          const void* x, const void* router, int width, int x_is_bf16, float* logits_out, cudaStream_t stream) {
+                          const void* x, const void* router, int width, int x_is_bf16, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192 || tile_rows <= 0) return (int)cudaErrorInvalidValue;
-    if (!logits && !(x && router && logits_out)) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+    if (!logits && !(x && router && (long long)n_tokens * n_experts <= 8192)) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int) + (logits ? 0 : (size_t)n_tokens * n_experts * sizeof(float));
     return (int)launch_pdl(moe_plan_kernel, dim3(1), dim3(MOE_PLAN_THREADS), smem, stream, logits, n_tokens, n_experts, top,
                            softmax_scores, renormalize, pair_expert, pair_weight, sorted_token, sorted_weight, dest, offsets,
-                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16,
-                           logits_out);
+                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16);
 }
 
 QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token, const float* sorted_weight, void* out,

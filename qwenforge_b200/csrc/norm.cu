@@ -239,11 +239,69 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
         o[c] = Num<T>::from_f(h[c] * inv_h * Num<T>::to_f(next_weight[c]));
 }
 
+// Narrow rows (width <= 32 * SWW_KEEP): a warp per row, eight rows per block; the row stays in the lanes' registers and both
+// sums of squares need shuffles only (no block-wide barrier), which is what a step of a few rows waits for.
+#define SWW_KEEP 32
+template <typename T>
+__global__ void __launch_bounds__(256)
+sandwich_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
+                          const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int rows, int width,
+                          const int* __restrict__ dest, int top, const float* __restrict__ row_weight) {
+    grid_chain_entry();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float* h = hidden + (size_t)row * width;
+    float kept[SWW_KEEP], hv[SWW_KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < SWW_KEEP; ++u) {
+        const int c = lane + 32 * u;
+        float v = 0.f;
+        if (c < width) {
+            hv[u] = h[c];
+            if (!dest) {
+                v = Num<T>::to_f(y[(size_t)row * width + c]);
+            } else {
+                for (int k = 0; k < top; ++k) {   // the same few words for every lane and column: they stay in the L1
+                    const int r = dest[(size_t)row * top + k];
+                    v += Num<T>::to_f(y[(size_t)r * width + c]) * (row_weight ? row_weight[r] : 1.f);
+                }
+            }
+        }
+        kept[u] = v;
+        ss += v * v;
+    }
+    const float inv_y = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_post);
+    ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < SWW_KEEP; ++u) {
+        const int c = lane + 32 * u;
+        if (c < width) {
+            kept[u] = hv[u] + kept[u] * inv_y * Num<T>::to_f(post_weight[c]);
+            h[c] = kept[u];
+            ss += kept[u] * kept[u];
+        }
+    }
+    if (!next_weight) return;
+    const float inv_h = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_next);
+    T* o = out + (size_t)row * width;
+#pragma unroll
+    for (int u = 0; u < SWW_KEEP; ++u) {
+        const int c = lane + 32 * u;
+        if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * Num<T>::to_f(next_weight[c]));
+    }
+}
+
 template <typename T>
 static int sandwich_launch(float* hidden, const void* y, const void* post_weight, float eps_post, const void* next_weight,
                            float eps_next, void* out, int rows, int width, const int* dest, int top, const float* row_weight,
                            cudaStream_t stream) {
     if (rows <= 0) return 0;
+    // which kernel runs depends on the width alone, so a row's result does not depend on how many rows the step has
+    if (width <= 32 * SWW_KEEP)
+        return (int)launch_pdl(sandwich_norm_warp_kernel<T>, dim3((rows + 7) / 8), dim3(256), 0, stream, hidden, (const T*)y,
+                               (const T*)post_weight, eps_post, (const T*)next_weight, eps_next, (T*)out, rows, width, dest, top,
+                               row_weight);
     return (int)launch_pdl(sandwich_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y, (const T*)post_weight,
                            eps_post, (const T*)next_weight, eps_next, (T*)out, width, dest, top, row_weight);
 }

@@ -1146,21 +1146,20 @@ def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = Fa
     if logits is not None:
         _dev("logits", logits, torch.float32)
         n_tokens, n_experts = logits.shape
-        width, scratch = 0, None
+        width = 0
     else:
         _dev("x", x)
         _dev("router", router, x.dtype)
         (n_tokens, width), n_experts = x.shape, router.shape[0]
         if router.shape[1] != width or n_tokens * n_experts > MOE_FUSED_ROUTER_MAX:
             raise KernelError("moe_plan: x [T, W] and router [E, W] with T * E <= %d, or give the logits" % MOE_FUSED_ROUTER_MAX)
-        scratch = torch.empty((n_tokens, n_experts), dtype=torch.float32, device=x.device)
     plan = MoePlan(n_tokens, n_experts, top, (logits if logits is not None else x).device, tile_rows)
     code = library("moe").qf_moe_plan(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
                                       _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
                                       _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),
                                       _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
                                       _I(tile_rows), _ptr(x if logits is None else None), _ptr(router if logits is None else None),
-                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _ptr(scratch), _stream())
+                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _stream())
     if code == 1:
         raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16, experts <= 8192)")
     _check(code, "moe_plan")
