@@ -14,29 +14,56 @@ latent_norm_cache_kernel(const float* __restrict__ down, int ld, int q_rank, int
                          const T* __restrict__ kv_norm, float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ slots, T* __restrict__ q_latent, T* __restrict__ latent_out, KvSite<T> site,
                          int write_cache, int* err) {
-    grid_chain_entry();
+    // the norm weights are nobody's output: a thread's first few are fetched before the wait for the kernel before this one
+    grid_launch_dependents();
+    constexpr int AHEAD = 4;
+    float qw[AHEAD], kw[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+        const int c = threadIdx.x + u * 128;
+        qw[u] = c < q_rank ? Num<T>::to_f(q_norm[c]) : 0.f;
+        kw[u] = c < kv_rank ? Num<T>::to_f(kv_norm[c]) : 0.f;
+    }
+    grid_dependency_wait();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const float* row = down + (size_t)t * ld;
+    // where the latent goes: a chain of three dependent loads, started before the sums so that it runs under them
+    T* cache_row = nullptr;
+    const int slot = slots[tok_seq[t]];
+    bool no_page = false;
+    if (write_cache && slot >= 0) {
+        cache_row = kv_row(site, slot, tok_pos[t], 0, 0);
+        no_page = cache_row == nullptr;
+    }
     if (q_rank > 0) {
         float ss = 0.f;
         for (int c = threadIdx.x; c < q_rank; c += blockDim.x) ss += row[c] * row[c];
         const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)q_rank + eps);
         T* dst = q_latent + (size_t)t * q_rank;
-        for (int c = threadIdx.x; c < q_rank; c += blockDim.x) dst[c] = Num<T>::from_f(row[c] * inv * Num<T>::to_f(q_norm[c]));
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+            const int c = threadIdx.x + u * 128;
+            if (c < q_rank) dst[c] = Num<T>::from_f(row[c] * inv * qw[u]);
+        }
+        for (int c = threadIdx.x + AHEAD * 128; c < q_rank; c += 128) dst[c] = Num<T>::from_f(row[c] * inv * Num<T>::to_f(q_norm[c]));
     }
     const float* kv = row + q_rank;
     float ss = 0.f;
     for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) ss += kv[c] * kv[c];
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)kv_rank + eps);
-    T* cache_row = nullptr;
-    const int slot = slots[tok_seq[t]];
-    if (write_cache && slot >= 0) {
-        cache_row = kv_row(site, slot, tok_pos[t], 0, 0);
-        if (!cache_row && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
-    }
+    if (no_page && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
     T* plain = latent_out ? latent_out + (size_t)t * kv_rank : nullptr;
-    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+        const int c = threadIdx.x + u * 128;
+        if (c < kv_rank) {
+            const T v = Num<T>::from_f(kv[c] * inv * kw[u]);
+            if (cache_row) cache_row[c] = v;
+            if (plain) plain[c] = v;
+        }
+    }
+    for (int c = threadIdx.x + AHEAD * 128; c < kv_rank; c += 128) {
         const T v = Num<T>::from_f(kv[c] * inv * Num<T>::to_f(kv_norm[c]));
         if (cache_row) cache_row[c] = v;
         if (plain) plain[c] = v;

@@ -179,31 +179,58 @@ QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, lon
 // per row; a thread keeps up to SW_KEEP of the row's elements in registers between the passes, wider rows are read again.
 // With `dest`, row t of y is not stored anywhere: it is the sum of `top` rows y[dest[t * top + k]] (each times
 // row_weight[that row], if given), summed in float32 in the order of k: what a mixture of experts leaves per token.
+// The rows' numbers and weights are read once, before anything that depends on them, so that all of a thread's loads of
+// the stream and of y are on their way together: a step of a few rows waits for this kernel's chain of loads, not for bytes.
 #define SW_KEEP 16
+#define SW_SRC 4     // rows summed per token in the kernel's fast form (more take the plain loop)
 template <typename T>
 __global__ void __launch_bounds__(256)
 sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
                      const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int width,
                      const int* __restrict__ dest, int top, const float* __restrict__ row_weight) {
-    grid_chain_entry();
+    // The norm weights are nobody's output: they are fetched before this kernel waits for the one before it, and so are no
+    // longer part of the chain of loads that follows.
+    grid_launch_dependents();
+    float pw[SW_KEEP], nw[SW_KEEP];
+#pragma unroll
+    for (int u = 0; u < SW_KEEP; ++u) {
+        const int c = threadIdx.x + u * 256;
+        pw[u] = c < width ? Num<T>::to_f(post_weight[c]) : 0.f;
+        nw[u] = (next_weight && c < width) ? Num<T>::to_f(next_weight[c]) : 0.f;
+    }
+    grid_dependency_wait();
     __shared__ float scratch[33];
     float* h = hidden + (size_t)blockIdx.x * width;
-    const T* yr = y + (size_t)blockIdx.x * width;
+    const int n_src = dest ? top : 1;
+    const bool few = n_src <= SW_SRC;
+    const T* src[SW_SRC];
+    float w[SW_SRC];
+#pragma unroll
+    for (int k = 0; k < SW_SRC; ++k) {
+        const bool on = few && k < n_src;
+        const int r = on ? (dest ? dest[(size_t)blockIdx.x * top + k] : (int)blockIdx.x) : 0;
+        src[k] = y + (size_t)r * width;
+        w[k] = on ? ((dest && row_weight) ? row_weight[r] : 1.f) : 0.f;
+    }
     auto y_at = [&](int c) -> float {
-        if (!dest) return Num<T>::to_f(yr[c]);
         float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int row = dest[(size_t)blockIdx.x * top + k];
-            const float v = Num<T>::to_f(y[(size_t)row * width + c]);
-            sum += row_weight ? v * row_weight[row] : v;
+        if (few) {
+#pragma unroll
+            for (int k = 0; k < SW_SRC; ++k) sum += k < n_src ? Num<T>::to_f(src[k][c]) * w[k] : 0.f;
+        } else {
+            for (int k = 0; k < top; ++k) {
+                const int r = dest[(size_t)blockIdx.x * top + k];
+                sum += Num<T>::to_f(y[(size_t)r * width + c]) * (row_weight ? row_weight[r] : 1.f);
+            }
         }
         return sum;
     };
-    float kept[SW_KEEP];
+    float kept[SW_KEEP], hv[SW_KEEP];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < SW_KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
+        hv[u] = c < width ? h[c] : 0.f;
         kept[u] = c < width ? y_at(c) : 0.f;
         ss += kept[u] * kept[u];
     }
@@ -217,7 +244,7 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
     for (int u = 0; u < SW_KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
         if (c < width) {
-            kept[u] = h[c] + kept[u] * inv_y * Num<T>::to_f(post_weight[c]);
+            kept[u] = hv[u] + kept[u] * inv_y * pw[u];
             h[c] = kept[u];
             ss += kept[u] * kept[u];
         }
@@ -233,63 +260,10 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
 #pragma unroll
     for (int u = 0; u < SW_KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
-        if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * Num<T>::to_f(next_weight[c]));
+        if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * nw[u]);
     }
     for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256)   // each thread re-reads the columns it wrote itself
         o[c] = Num<T>::from_f(h[c] * inv_h * Num<T>::to_f(next_weight[c]));
-}
-
-// Narrow rows (width <= 32 * SWW_KEEP): a warp per row, eight rows per block; the row stays in the lanes' registers and both
-// sums of squares need shuffles only (no block-wide barrier), which is what a step of a few rows waits for.
-#define SWW_KEEP 32
-template <typename T>
-__global__ void __launch_bounds__(256)
-sandwich_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
-                          const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int rows, int width,
-                          const int* __restrict__ dest, int top, const float* __restrict__ row_weight) {
-    grid_chain_entry();
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    float* h = hidden + (size_t)row * width;
-    float kept[SWW_KEEP], hv[SWW_KEEP];
-    float ss = 0.f;
-#pragma unroll
-    for (int u = 0; u < SWW_KEEP; ++u) {
-        const int c = lane + 32 * u;
-        float v = 0.f;
-        if (c < width) {
-            hv[u] = h[c];
-            if (!dest) {
-                v = Num<T>::to_f(y[(size_t)row * width + c]);
-            } else {
-                for (int k = 0; k < top; ++k) {   // the same few words for every lane and column: they stay in the L1
-                    const int r = dest[(size_t)row * top + k];
-                    v += Num<T>::to_f(y[(size_t)r * width + c]) * (row_weight ? row_weight[r] : 1.f);
-                }
-            }
-        }
-        kept[u] = v;
-        ss += v * v;
-    }
-    const float inv_y = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_post);
-    ss = 0.f;
-#pragma unroll
-    for (int u = 0; u < SWW_KEEP; ++u) {
-        const int c = lane + 32 * u;
-        if (c < width) {
-            kept[u] = hv[u] + kept[u] * inv_y * Num<T>::to_f(post_weight[c]);
-            h[c] = kept[u];
-            ss += kept[u] * kept[u];
-        }
-    }
-    if (!next_weight) return;
-    const float inv_h = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_next);
-    T* o = out + (size_t)row * width;
-#pragma unroll
-    for (int u = 0; u < SWW_KEEP; ++u) {
-        const int c = lane + 32 * u;
-        if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * Num<T>::to_f(next_weight[c]));
-    }
 }
 
 template <typename T>
@@ -297,11 +271,6 @@ static int sandwich_launch(float* hidden, const void* y, const void* post_weight
                            float eps_next, void* out, int rows, int width, const int* dest, int top, const float* row_weight,
                            cudaStream_t stream) {
     if (rows <= 0) return 0;
-    // which kernel runs depends on the width alone, so a row's result does not depend on how many rows the step has
-    if (width <= 32 * SWW_KEEP)
-        return (int)launch_pdl(sandwich_norm_warp_kernel<T>, dim3((rows + 7) / 8), dim3(256), 0, stream, hidden, (const T*)y,
-                               (const T*)post_weight, eps_post, (const T*)next_weight, eps_next, (T*)out, rows, width, dest, top,
-                               row_weight);
     return (int)launch_pdl(sandwich_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y, (const T*)post_weight,
                            eps_post, (const T*)next_weight, eps_next, (T*)out, width, dest, top, row_weight);
 }
