@@ -176,47 +176,37 @@ QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, lon
 // A sublayer's output normalised on its way into the stream, and the stream normalised again for the next sublayer:
 //   hidden += y * rsqrt(mean(y^2) + eps_post) * post_weight;   out = hidden * rsqrt(mean(hidden^2) + eps_next) * next_weight
 // (the second half only when next_weight is given). Both sums of squares, both roots and the addition are float32. A block
-// per row; a thread keeps up to SW_KEEP of the row's elements in registers between the passes, wider rows are read again.
+// per row; a thread keeps KEEP of the row's elements in registers between the passes (KEEP x 256 >= width for rows of up to
+// 4,096 columns; wider rows are read again).
 // With `dest`, row t of y is not stored anywhere: it is the sum of `top` rows y[dest[t * top + k]] (each times
 // row_weight[that row], if given), summed in float32 in the order of k: what a mixture of experts leaves per token.
-// The rows' numbers and weights are read once, before anything that depends on them, so that all of a thread's loads of
-// the stream and of y are on their way together: a step of a few rows waits for this kernel's chain of loads, not for bytes.
-#define SW_KEEP 16
-#define SW_SRC 4     // rows summed per token in the kernel's fast form (more take the plain loop)
-template <typename T>
+// NSRC is how many rows are summed, known when the kernel is chosen (1, 2, up to 4; 0: any number, by a loop), so that
+// a thread's loads of the stream, of y and of both norm weights are few and all on their way together: a step of a few
+// rows waits for this kernel's chain of loads, a step of thousands for its bytes, and neither should wait for instructions.
+template <typename T, int KEEP, int NSRC>
 __global__ void __launch_bounds__(256)
 sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const T* __restrict__ post_weight, float eps_post,
                      const T* __restrict__ next_weight, float eps_next, T* __restrict__ out, int width,
                      const int* __restrict__ dest, int top, const float* __restrict__ row_weight) {
-    // The norm weights are nobody's output: they are fetched before this kernel waits for the one before it, and so are no
-    // longer part of the chain of loads that follows.
-    grid_launch_dependents();
-    float pw[SW_KEEP], nw[SW_KEEP];
-#pragma unroll
-    for (int u = 0; u < SW_KEEP; ++u) {
-        const int c = threadIdx.x + u * 256;
-        pw[u] = c < width ? Num<T>::to_f(post_weight[c]) : 0.f;
-        nw[u] = (next_weight && c < width) ? Num<T>::to_f(next_weight[c]) : 0.f;
-    }
-    grid_dependency_wait();
+    grid_chain_entry();
     __shared__ float scratch[33];
     float* h = hidden + (size_t)blockIdx.x * width;
+    constexpr int NS = NSRC > 0 ? NSRC : 1;
     const int n_src = dest ? top : 1;
-    const bool few = n_src <= SW_SRC;
-    const T* src[SW_SRC];
-    float w[SW_SRC];
+    const T* src[NS];
+    float w[NS];
 #pragma unroll
-    for (int k = 0; k < SW_SRC; ++k) {
-        const bool on = few && k < n_src;
+    for (int k = 0; k < NS; ++k) {
+        const bool on = NSRC > 0 && k < n_src;
         const int r = on ? (dest ? dest[(size_t)blockIdx.x * top + k] : (int)blockIdx.x) : 0;
         src[k] = y + (size_t)r * width;
         w[k] = on ? ((dest && row_weight) ? row_weight[r] : 1.f) : 0.f;
     }
     auto y_at = [&](int c) -> float {
         float sum = 0.f;
-        if (few) {
+        if (NSRC > 0) {
 #pragma unroll
-            for (int k = 0; k < SW_SRC; ++k) sum += k < n_src ? Num<T>::to_f(src[k][c]) * w[k] : 0.f;
+            for (int k = 0; k < NS; ++k) sum += (NSRC <= 2 || k < n_src) ? Num<T>::to_f(src[k][c]) * w[k] : 0.f;
         } else {
             for (int k = 0; k < top; ++k) {
                 const int r = dest[(size_t)blockIdx.x * top + k];
@@ -225,23 +215,26 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
         }
         return sum;
     };
-    float kept[SW_KEEP], hv[SW_KEEP];
+    float kept[KEEP], hv[KEEP], pw[KEEP], nw[KEEP];
     float ss = 0.f;
 #pragma unroll
-    for (int u = 0; u < SW_KEEP; ++u) {
+    for (int u = 0; u < KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
-        hv[u] = c < width ? h[c] : 0.f;
-        kept[u] = c < width ? y_at(c) : 0.f;
+        const bool ok = c < width;
+        hv[u] = ok ? h[c] : 0.f;
+        kept[u] = ok ? y_at(c) : 0.f;
+        pw[u] = ok ? Num<T>::to_f(post_weight[c]) : 0.f;
+        nw[u] = (ok && next_weight) ? Num<T>::to_f(next_weight[c]) : 0.f;
         ss += kept[u] * kept[u];
     }
-    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
+    for (int c = threadIdx.x + KEEP * 256; c < width; c += 256) {
         const float v = y_at(c);
         ss += v * v;
     }
     const float inv_y = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_post);
     ss = 0.f;
 #pragma unroll
-    for (int u = 0; u < SW_KEEP; ++u) {
+    for (int u = 0; u < KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
         if (c < width) {
             kept[u] = hv[u] + kept[u] * inv_y * pw[u];
@@ -249,7 +242,7 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
             ss += kept[u] * kept[u];
         }
     }
-    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256) {
+    for (int c = threadIdx.x + KEEP * 256; c < width; c += 256) {
         const float v = h[c] + y_at(c) * inv_y * Num<T>::to_f(post_weight[c]);
         h[c] = v;
         ss += v * v;
@@ -258,21 +251,41 @@ sandwich_norm_kernel(float* __restrict__ hidden, const T* __restrict__ y, const 
     const float inv_h = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_next);
     T* o = out + (size_t)blockIdx.x * width;
 #pragma unroll
-    for (int u = 0; u < SW_KEEP; ++u) {
+    for (int u = 0; u < KEEP; ++u) {
         const int c = threadIdx.x + u * 256;
         if (c < width) o[c] = Num<T>::from_f(kept[u] * inv_h * nw[u]);
     }
-    for (int c = threadIdx.x + SW_KEEP * 256; c < width; c += 256)   // each thread re-reads the columns it wrote itself
+    for (int c = threadIdx.x + KEEP * 256; c < width; c += 256)   // each thread re-reads the columns it wrote itself
         o[c] = Num<T>::from_f(h[c] * inv_h * Num<T>::to_f(next_weight[c]));
 }
 
+template <typename T, int KEEP>
+static int sandwich_launch_keep(float* hidden, const void* y, const void* post_weight, float eps_post, const void* next_weight,
+                                float eps_next, void* out, int rows, int width, const int* dest, int top, const float* row_weight,
+                                cudaStream_t stream) {
+    const int n_src = dest ? top : 1;
+#define QF_SANDWICH(NSRC)                                                                                                    \
+    return (int)launch_pdl(sandwich_norm_kernel<T, KEEP, NSRC>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y,       \
+                           (const T*)post_weight, eps_post, (const T*)next_weight, eps_next, (T*)out, width, dest, top, row_weight)
+    if (n_src == 1) QF_SANDWICH(1);
+    if (n_src == 2) QF_SANDWICH(2);
+    if (n_src <= 4) QF_SANDWICH(4);
+    QF_SANDWICH(0);
+#undef QF_SANDWICH
+}
+
+// Which kernel runs depends on the width and on the number of rows summed alone, so a row's result does not depend on how
+// many rows the step has.
 template <typename T>
 static int sandwich_launch(float* hidden, const void* y, const void* post_weight, float eps_post, const void* next_weight,
                            float eps_next, void* out, int rows, int width, const int* dest, int top, const float* row_weight,
                            cudaStream_t stream) {
     if (rows <= 0) return 0;
-    return (int)launch_pdl(sandwich_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)y, (const T*)post_weight,
-                           eps_post, (const T*)next_weight, eps_next, (T*)out, width, dest, top, row_weight);
+    if (width <= 1024)
+        return sandwich_launch_keep<T, 4>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream);
+    if (width <= 2048)
+        return sandwich_launch_keep<T, 8>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream);
+    return sandwich_launch_keep<T, 16>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream);
 }
 
 // y, post_weight, next_weight (may be null) and out (null with it) share a dtype; hidden is float32 [rows, width]. dest
