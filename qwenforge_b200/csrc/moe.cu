@@ -21,6 +21,36 @@
 #define MOE_PLAN_THREADS 1024
 #define MOE_MAX_TOP 16
 
+// One token's choice: the `top` experts with the largest scores (the larger logit is the larger score; ties go to the
+// lower index) and their weights.
+__device__ __forceinline__ void moe_choose(const float* z, int n_experts, int top, int softmax_scores, int renormalize,
+                                           int* chosen, float* weight) {
+    float top_z = -FLT_MAX, denom = 1.f;
+    if (softmax_scores) {
+        for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z[e]);
+        denom = 0.f;
+        for (int e = 0; e < n_experts; ++e) denom += expf(z[e] - top_z);
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float best_z = -FLT_MAX;
+        for (int e = 0; e < n_experts; ++e) {
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
+            if (!taken && (best < 0 || z[e] > best_z)) {
+                best = e;
+                best_z = z[e];
+            }
+        }
+        chosen[k] = best;
+        weight[k] = softmax_scores ? expf(best_z - top_z) / denom : 1.0f / (1.0f + expf(-best_z));
+        total += weight[k];
+    }
+    if (renormalize)
+        for (int k = 0; k < top; ++k) weight[k] /= total;
+}
+
 // Scratch in pair order (pair = token * top + k): pair_expert, pair_weight. Results: dest [pairs] (the row of every pair),
 // and in row order sorted_token [pairs], sorted_weight float32 [pairs]; offsets [experts + 1]; tile_group, tile_row0
 // [max_tiles]; n_tiles [1].
@@ -76,35 +106,14 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
     __syncthreads();
     // pass 1: choose, and take a rank among the expert's rows
     for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
-        const float* z = logits + (size_t)t * n_experts;
-        float top_z = -FLT_MAX, denom = 1.f;
-        if (softmax_scores) {
-            for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z[e]);
-            denom = 0.f;
-            for (int e = 0; e < n_experts; ++e) denom += expf(z[e] - top_z);
-        }
         int chosen[MOE_MAX_TOP];
-        float weight[MOE_MAX_TOP], total = 0.f;
-        for (int k = 0; k < top; ++k) {
-            int best = -1;
-            float best_z = -FLT_MAX;
-            for (int e = 0; e < n_experts; ++e) {
-                bool taken = false;
-                for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
-                if (!taken && (best < 0 || z[e] > best_z)) {   // the larger logit is the larger score; ties go to the lower index
-                    best = e;
-                    best_z = z[e];
-                }
-            }
-            chosen[k] = best;
-            weight[k] = softmax_scores ? expf(best_z - top_z) / denom : 1.0f / (1.0f + expf(-best_z));
-            total += weight[k];
-        }
+        float weight[MOE_MAX_TOP];
+        moe_choose(logits + (size_t)t * n_experts, n_experts, top, softmax_scores, renormalize, chosen, weight);
         for (int k = 0; k < top; ++k) {
             const int pair = t * top + k;
             pair_expert[pair] = chosen[k];
             dest[pair] = atomicAdd(&counts[chosen[k]], 1);        // for now: the pair's rank among its expert's rows
-            pair_weight[pair] = renormalize ? weight[k] / total : weight[k];
+            pair_weight[pair] = weight[k];
         }
     }
     __syncthreads();
@@ -142,6 +151,79 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
     }
 }
 
+// The same plan for a long step, where one block would be what the step waits for: (1) blocks of 256 tokens choose and count
+// in shared memory, then reserve their rows of every expert with ONE atomic per block and expert on `expert_rows` (zero
+// before the launch); (2) one block turns the experts' row counts into offsets and tiles; (3) every pair goes to its row.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                 int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ dest,
+                 int* __restrict__ expert_rows) {
+    grid_chain_entry();
+    extern __shared__ int shared[];
+    int* counts = shared;               // [experts] pairs of this block
+    int* base = shared + n_experts;     // [experts] where this block's pairs start among the expert's rows
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    int chosen[MOE_MAX_TOP], rank[MOE_MAX_TOP];
+    float weight[MOE_MAX_TOP];
+    if (t < n_tokens) {
+        moe_choose(logits + (size_t)t * n_experts, n_experts, top, softmax_scores, renormalize, chosen, weight);
+        for (int k = 0; k < top; ++k) rank[k] = atomicAdd(&counts[chosen[k]], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) base[e] = counts[e] > 0 ? atomicAdd(&expert_rows[e], counts[e]) : 0;
+    __syncthreads();
+    if (t < n_tokens)
+        for (int k = 0; k < top; ++k) {
+            const int pair = t * top + k;
+            pair_expert[pair] = chosen[k];
+            dest[pair] = base[chosen[k]] + rank[k];
+            pair_weight[pair] = weight[k];
+        }
+}
+
+__global__ void __launch_bounds__(256)
+moe_offsets_kernel(const int* __restrict__ expert_rows, int n_experts, int* __restrict__ offsets, int* __restrict__ tile_group,
+                   int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles, int tile_rows) {
+    grid_chain_entry();
+    extern __shared__ int shared[];
+    int* first_row = shared;                 // [experts]
+    int* first_tile = shared + n_experts;    // [experts + 1]
+    if (threadIdx.x == 0) {
+        int row = 0, tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            const int n = expert_rows[e];
+            offsets[e] = row;
+            first_row[e] = row;
+            first_tile[e] = tile;
+            row += n;
+            tile += (n + tile_rows - 1) / tile_rows;
+        }
+        offsets[n_experts] = row;
+        first_tile[n_experts] = tile;
+        n_tiles[0] = tile < max_tiles ? tile : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        for (int i = first_tile[e]; i < first_tile[e + 1] && i < max_tiles; ++i) {
+            tile_group[i] = e;
+            tile_row0[i] = first_row[e] + (i - first_tile[e]) * tile_rows;
+        }
+}
+
+__global__ void __launch_bounds__(256)
+moe_place_kernel(const int* __restrict__ pair_expert, const float* __restrict__ pair_weight, const int* __restrict__ offsets,
+                 int* __restrict__ dest, int* __restrict__ sorted_token, float* __restrict__ sorted_weight, int pairs, int top) {
+    grid_chain_entry();
+    const int pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= pairs) return;
+    const int row = offsets[pair_expert[pair]] + dest[pair];
+    dest[pair] = row;
+    sorted_token[row] = pair / top;
+    sorted_weight[row] = pair_weight[pair];
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ sorted_token, const float* __restrict__ sorted_weight,
@@ -152,6 +234,12 @@ moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ sorted_token,
     const T* src = x + (size_t)sorted_token[r] * width;
     const float w = scale_input ? sorted_weight[r] : 1.f;
     T* dst = out + (size_t)r * width;
+    if (!scale_input && ((size_t)width * sizeof(T)) % 16 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);   // a plain copy of the row, 16 bytes at a time
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int c = threadIdx.x; c < (int)((size_t)width * sizeof(T) / 16); c += blockDim.x) d4[c] = s4[c];
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = Num<T>::from_f(Num<T>::to_f(src[c]) * w);
 }
 
@@ -208,4 +296,24 @@ QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const 
                                (bf16*)out, n_tokens, top, width, scale_output);
     return (int)launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)y, dest, sorted_weight,
                            (float*)out, n_tokens, top, width, scale_output);
+}
+
+// The plan of a long step by three launches (see moe_route_kernel). expert_rows: int32 [n_experts], zero before the call.
+QF_EXPORT int qf_moe_plan_long(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                               int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                               int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                               int* expert_rows, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 4096 || tile_rows <= 0 || !logits || !expert_rows)
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+    int code = (int)launch_pdl(moe_route_kernel, dim3((n_tokens + 255) / 256), dim3(256), smem, stream, logits, n_tokens, n_experts,
+                               top, softmax_scores, renormalize, pair_expert, pair_weight, dest, expert_rows);
+    if (code) return code;
+    code = (int)launch_pdl(moe_offsets_kernel, dim3(1), dim3(256), smem, stream, (const int*)expert_rows, n_experts, offsets,
+                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows);
+    if (code) return code;
+    const int pairs = n_tokens * top;
+    return (int)launch_pdl(moe_place_kernel, dim3((pairs + 255) / 256), dim3(256), 0, stream, (const int*)pair_expert,
+                           (const float*)pair_weight, (const int*)offsets, dest, sorted_token, sorted_weight, pairs, top);
 }

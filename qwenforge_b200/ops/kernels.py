@@ -1102,6 +1102,7 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> Non
 GROUP_TILE_ROWS = 64          # rows of a tile of the grouped products (QF_GROUP_BM in csrc/common.cuh)
 GROUP_LARGE_TILE_ROWS = 128   # and of the large tile, for bfloat16 operands with rows enough
 MOE_FUSED_ROUTER_MAX = 4096   # tokens x experts up to which the plan's one block makes the router's logits itself
+MOE_LONG_PLAN_TOKENS = 1024   # tokens from which the plan is made by three parallel launches instead of one block
 
 
 class MoePlan:
@@ -1154,6 +1155,17 @@ def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = Fa
         if router.shape[1] != width or n_tokens * n_experts > MOE_FUSED_ROUTER_MAX:
             raise KernelError("moe_plan: x [T, W] and router [E, W] with T * E <= %d, or give the logits" % MOE_FUSED_ROUTER_MAX)
     plan = MoePlan(n_tokens, n_experts, top, (logits if logits is not None else x).device, tile_rows)
+    if logits is not None and n_tokens >= MOE_LONG_PLAN_TOKENS and n_experts <= 4096:
+        expert_rows = torch.zeros(n_experts, dtype=torch.int32, device=logits.device)
+        code = library("moe").qf_moe_plan_long(
+            _ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)), _I(int(renormalize)),
+            _ptr(plan.pair_expert), _ptr(plan.pair_weight), _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest),
+            _ptr(plan.offsets), _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
+            _I(tile_rows), _ptr(expert_rows), _stream())
+        if code == 1:
+            raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16)")
+        _check(code, "moe_plan")
+        return plan
     code = library("moe").qf_moe_plan(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
                                       _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
                                       _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),

@@ -138,7 +138,7 @@ def test_head_linear(dtype, shape):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(37, 5, 2, 52, 22), (300, 6, 3, 128, 64), (1, 4, 1, 96, 40), (130, 3, 3, 40, 24),
-                                   (1500, 4, 2, 128, 72), (900, 3, 1, 200, 136)])
+                                   (1500, 4, 2, 128, 72), (900, 3, 1, 200, 136), (1024, 70, 4, 64, 24)])
 def test_routing_and_expert_products(dtype, shape):
     """Routing, sorting by expert, the gathered rows, both grouped products and the combination, against the references;
     with an expert that nobody chooses and one that nearly everybody does."""
@@ -153,7 +153,7 @@ def test_routing_and_expert_products(dtype, shape):
     w1 = (torch.randn(experts, 2 * ff, width, generator=g) / math.sqrt(width)).to(dtype).to(DEV)
     w2 = (torch.randn(experts, width, ff, generator=g) / math.sqrt(ff)).to(dtype).to(DEV)
     tile_rows = ops.moe_tile_rows(tokens, experts, top, w1)   # 128 for the two largest shapes in bfloat16
-    assert tile_rows == (128 if dtype == torch.bfloat16 and tokens >= 900 else 64)
+    assert tile_rows == (128 if dtype == torch.bfloat16 and tokens >= 900 and experts < 10 else 64)
     plan, want_plan = ops.moe_plan(logits, top, tile_rows=tile_rows), refs.moe_plan(logits.cpu(), top)
     offsets = plan.offsets.cpu().tolist()
     counts = torch.bincount(want_plan.row_expert, minlength=experts).tolist()
