@@ -71,7 +71,7 @@ def test_embed_positions(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [52, 320, 5000])
+@pytest.mark.parametrize("width", [52, 328, 1500, 5000])
 def test_sandwich_norm(dtype, width):
     from qwenforge_b200 import ops
     g = torch.Generator().manual_seed(width)
