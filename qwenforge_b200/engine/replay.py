@@ -75,7 +75,7 @@ def replay(model: Model, cache, lines, out_dir: Path, report=print, dump_dir: Pa
             entries.append((slots[key], [int(t) for t in item["tokens"]]))
             want.append([int(w) for w in item.get("want", [])])
             held[key] = held.get(key, 0) + len(item["tokens"])
-        if max_tokens is not None and sum(held.values()) > max_tokens:
+        if max_tokens is not None and sum(held.values()) > round_up(max_tokens, PAGE_TOKENS):   # (a page of tolerance)
             raise CacheFull(f"step {step}: live requests would hold {sum(held.values())} tokens, --max-tokens is {max_tokens}")
         if entries:
             logits = model.step(cache, entries, want)

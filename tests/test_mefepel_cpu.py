@@ -100,3 +100,19 @@ def test_the_latent_cache_holds_one_plane(reference_kernels, tmp_path):
     assert all(g.storage.shape[2] == 1 for g in cache.kv_groups)
     # what a decode step reads: rank numbers per position and layer, not heads * (dim + vdim)
     assert cache.read_bytes([100]) == 100 * (36 * 2 + 44) * 4
+
+
+@pytest.mark.parametrize("order", ["none_last", "none_first", "only_none"])
+def test_layers_without_a_feed_forward_at_either_end(reference_kernels, order, tmp_path):
+    from tests.helpers_mefepel import config, dense, layer, mixer, moe
+    with_ff = [layer(mixer(2, 6, 10, 20, 12, 0.3), moe(14, 3, 3)), layer(mixer(3, 4, 4, 12, 8, 0.5), dense(30, 1.1))]
+    bare = layer(mixer(2, 8, 6, 16, 10, 0.35), None)
+    layers = {"none_last": with_ff + [bare], "none_first": [bare] + with_ff, "only_none": [bare, bare]}[order]
+    cfg = config(90, 28, 80, 2e-5, layers)
+    model, weights, _ = build(cfg, tmp_path, seed=9)
+    cache = model.new_cache(128, 2)
+    tokens = random_tokens(cfg["vocab"], 30, 3)
+    slot = cache.open()
+    first = model.step(cache, [(slot, tokens[:19])], want=[list(range(19))])
+    rest = [model.step(cache, [(slot, [t])]) for t in tokens[19:]]
+    assert max_err(torch.cat([first] + rest), plain.forward_logits(cfg, weights, tokens)) < 5e-5

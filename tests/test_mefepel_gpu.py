@@ -92,10 +92,11 @@ def test_sandwich_norm(dtype, width):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("weighted", [False, True])
-def test_sandwich_norm_sums_a_tokens_rows_on_the_way_in(dtype, weighted):
+@pytest.mark.parametrize("top,width", [(3, 200), (2, 1100), (6, 72), (1, 2500)])
+def test_sandwich_norm_sums_a_tokens_rows_on_the_way_in(dtype, weighted, top, width):
     from qwenforge_b200 import ops
     g = torch.Generator().manual_seed(5)
-    tokens, top, width = 9, 3, 200
+    tokens = 9
     hidden = torch.randn(tokens, width, generator=g).to(DEV)
     rows = torch.randn(tokens * top, width, generator=g).to(dtype).to(DEV)
     dest = torch.randperm(tokens * top, generator=g).int().to(DEV)
@@ -501,6 +502,23 @@ def test_a_long_prompt_takes_the_tensor_core_experts(tmp_path):
     got = run_cuts(model, cache, tokens, [1600])
     want = plain.forward_logits(cfg, weights, tokens)
     logits_close(got[::7], want[::7], torch.bfloat16, "long prompt", plain.router_margins(cfg, weights, tokens)[::7])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("order", ["none_last", "none_first", "only_none"])
+def test_layers_without_a_feed_forward_at_either_end(order, dtype, tmp_path):
+    """The last post-norm of the model has no next layer to ride on, and a layer without a feed-forward hands its mixer's
+    output straight to the next layer's first norm."""
+    with_ff = [layer(mixer(2, 16, 24, 32, 40, 0.3), moe(24, 3, 3)), layer(mixer(3, 8, 8, 96, 16, 0.5), dense(56, 1.1))]
+    bare = layer(mixer(5, 8, 6, 64, 24, 0.35), None)
+    layers = {"none_last": with_ff + [bare], "none_first": [bare] + with_ff, "only_none": [bare, bare]}[order]
+    cfg = config(190, 40, 400, 2e-5, layers)
+    model, weights, _ = build(cfg, tmp_path, dtype, seed=9)
+    cache = model.new_cache(64 * 8, 2)
+    tokens = random_tokens(cfg["vocab"], 150, 3)
+    got = run_cuts(model, cache, tokens, [120] + [1] * 30)
+    logits_close(got, plain.forward_logits(cfg, weights, tokens), torch.float32 if dtype == "float32" else torch.bfloat16, order,
+                 plain.router_margins(cfg, weights, tokens))
 
 
 def _far_key_model(kind):
