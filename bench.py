@@ -3,6 +3,8 @@
 decode at batch 1 and 64, and the same decode rate end to end through the Python entry point.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --design mefepel     # instead: the Mefepel presets beside the Qwen2 presets of equal layer sizes
+                                         # (prompt and decode rates, device times by kind of kernel), as one JSON line
 
 One decode step = one token for every sequence of the batch. The K timed steps are the last K steps before
 the context length is reached, so the cache is read at (almost) its full length. Timed with CUDA events on
