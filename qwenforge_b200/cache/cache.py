@@ -6,8 +6,9 @@ starts takes it again.
 
 What is kept per slot is declared by the model's mixers, one *need* per schedule entry:
 
-  KvNeed     keys and values of every position (window 0) or of the last `window` positions (or one row per
-             position that serves as both, `planes=1`).
+  KvNeed     keys and values of every position (window 0), of the last `window` positions, or of the positions of
+             the current block of `chunk` (a mask that cuts a sequence into blocks counted from its position 0); or
+             one row per position that serves as both, `planes=1`.
              Storage is handed out in pages of PAGE_TOKENS positions, so a sequence holds
              ceil(length / PAGE_TOKENS) pages and nothing more: the cache is sized by the
              number of live tokens, not by slots x longest sequence.
@@ -45,6 +46,21 @@ class KvNeed:
     window: int = 0  # 0: every earlier position
     planes: int = 2  # rows kept per position and head: keys and values, or 1 for a mixer whose keys are its values
                      # (the shared latent of a latent attention)
+    chunk: int = 0   # > 0: a query sees only the positions of its own block of `chunk` positions
+
+    def first_visible(self, position: int) -> int:
+        """Lowest position that a query at `position` sees."""
+        first = max(0, position - self.window + 1) if self.window > 0 else 0
+        return max(first, position // self.chunk * self.chunk) if self.chunk > 0 else first
+
+    def merged(self, other: "KvNeed") -> "KvNeed":
+        """What serves this need and a reader with a mask of its own over the same rows: where the masks differ, every
+        position is kept."""
+        if (other.kv_heads, other.head_dim, other.planes) != (self.kv_heads, self.head_dim, self.planes):
+            raise ValueError(f"a layer that reads another layer's cache needs rows of the same shape: {other} against {self}")
+        if (other.window, other.chunk) == (self.window, self.chunk):
+            return self
+        return KvNeed(self.kv_heads, self.head_dim, 0, self.planes, 0)
 
 
 @dataclass(frozen=True)
@@ -89,7 +105,7 @@ class KvGroup:
 
     def first_needed(self, length: int) -> int:
         """Lowest position that a query at position >= length can still see."""
-        return max(0, length - self.need.window + 1) if self.need.window > 0 else 0
+        return self.need.first_visible(length)
 
     def grant(self, slot: int, logical_pages: Sequence[int]) -> None:
         ids = self.pages.take(len(logical_pages))
@@ -105,7 +121,7 @@ class KvGroup:
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages all of whose positions have left the window of every later query."""
-        if self.need.window <= 0:
+        if self.need.window <= 0 and self.need.chunk <= 0:
             return
         keep_from = self.first_needed(length) // PAGE_TOKENS
         gone = [lp for lp in self._held[slot] if lp < keep_from]
@@ -285,7 +301,7 @@ class SequenceCache:
         total = 0
         for g in self.kv_groups:
             per_token = len(g.entries) * g.need.planes * g.need.kv_heads * g.need.head_dim * g.storage.element_size()
-            total += per_token * sum(min(n, g.need.window) if g.need.window > 0 else n for n in lengths)
+            total += per_token * sum(n - g.need.first_visible(n - 1) for n in lengths if n > 0)
         return total
 
     def storage_bytes(self) -> int:

@@ -70,7 +70,12 @@ class Model:
 
     def cache_needs(self) -> list:
         """Per schedule entry: what its mixer keeps per sequence; None when it reads another entry's cache."""
-        return [None if e.cache_from is not None else self.blocks[e.layer].cache_need() for e in self.spec.schedule]
+        needs = [None if e.cache_from is not None else self.blocks[e.layer].cache_need() for e in self.spec.schedule]
+        for e in self.spec.schedule:   # a reader with a mask of its own widens what its source keeps
+            own = self.blocks[e.layer].cache_need() if e.cache_from is not None else None
+            if own is not None and hasattr(needs[e.cache_from], "merged"):
+                needs[e.cache_from] = needs[e.cache_from].merged(own)
+        return needs
 
     # ------------------------------------------------------------------ weights
     def bind(self, tensors) -> "Model":

@@ -203,8 +203,12 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
 
 def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
                      inv_freq: Optional[torch.Tensor], rot_dim: int, n_heads: int, q_out: torch.Tensor,
-                     site: KvSiteArgs, write_cache: bool, err: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
-    """Rotate q and k heads of qkv [T, (NH + 2 KVH) D] by position, write q to q_out [T, NH D] and k, v into the cache."""
+                     site: KvSiteArgs, write_cache: bool, err: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     unit_norm_eps: Optional[float] = None, norm_dim: int = 0, has_kv: bool = True) -> None:
+    """Rotate q and k heads of qkv [T, (NH + 2 KVH) D] by position, write q to q_out [T, NH D] and k, v into the cache.
+    `unit_norm_eps`: after the rotation every q and k head is divided by its root mean square (float32), the mean taken
+    over the head's first `norm_dim` components (0: all; a head padded with zeros beyond its own size names that size).
+    `has_kv` false: the rows hold queries only, [T, NH D] (a layer that reads another layer's keys and values)."""
     _dev("qkv", qkv)
     _dev("q_out", q_out, qkv.dtype)
     _dev("cache", site.storage, qkv.dtype)
@@ -213,8 +217,10 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
     _dev("slots", slots, torch.int32)
     n = qkv.shape[0]
     d, kvh = site.head_dim, site.kv_heads
-    if qkv.shape[1] != (n_heads + 2 * kvh) * d or q_out.shape != (n, n_heads * d):
+    if qkv.shape[1] != (n_heads + (2 * kvh if has_kv else 0)) * d or q_out.shape != (n, n_heads * d):
         raise KernelError("rope_cache_write: qkv/q_out widths do not match the head counts")
+    if not has_kv and write_cache:
+        raise KernelError("rope_cache_write: rows without keys and values cannot write a cache")
     if bias is not None:
         _dev("bias", bias, qkv.dtype)
         if bias.numel() != qkv.shape[1]:
@@ -223,6 +229,16 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
         _dev("inv_freq", inv_freq, torch.float32)
         if inv_freq.numel() * 2 != rot_dim:
             raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 frequencies")
+    if unit_norm_eps is not None or not has_kv:
+        if not 0 <= norm_dim <= d:
+            raise KernelError("rope_cache_write: norm_dim must lie within the head size")
+        _check(library("rope_cache").qf_rope_norm_cache_write(
+            _I(_is_bf16(qkv.dtype)), _ptr(qkv), _ptr(bias), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
+            _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
+            _LL(site.page_elems), _I(site.table_stride), _I(kvh), _I(d), _I(1 if write_cache else 0), _I(1 if has_kv else 0),
+            _I(norm_dim or d), _F(-1.0 if unit_norm_eps is None else unit_norm_eps), _I(n), _ptr(err), _stream()),
+            "rope_cache_write")
+        return
     _check(library("rope_cache").qf_rope_cache_write(
         _I(_is_bf16(qkv.dtype)), _ptr(qkv), _ptr(bias), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
         _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
@@ -238,8 +254,10 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
                       window: int, err: torch.Tensor, scratch: Optional["DecodeScratch"] = None,
                       max_kv_len: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
-                      shared_values: bool = False) -> None:
+                      shared_values: bool = False, chunk: int = 0, softcap: float = 0.0) -> None:
     """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math).
+    `chunk` > 0: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0 of the
+    sequence). `softcap` > 0: a score s (after the scale) becomes softcap * tanh(s / softcap).
     `sinks` (float32 [n_heads]): a logit per head that joins the softmax's denominator once, with no key and no value.
     `shared_values`: the values are the keys themselves (a cache whose pages hold one plane).
     A step of one token per sequence whose longest sequence exceeds one chunk of 256 keys is cut into chunks of keys
@@ -261,17 +279,17 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
             and max_kv_len > GENERIC_DECODE_CHUNK):
         n_chunks = -(-int(max_kv_len) // GENERIC_DECODE_CHUNK)
         scratch.ensure(n_seqs, n_heads, n_chunks, d, 0)
-        _check(library("attention_generic").qf_attention_generic_decode_ex(
+        _check(library("attention_generic").qf_attention_generic_decode_masked(
             _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
             _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
             _I(n_seqs), _I(int(max_kv_len)), _F(scale), _I(window), _ptr(scratch.part_o), _ptr(scratch.part_ml), _ptr(err),
-            _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_generic")
+            _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _stream()), "attention_generic")
         return
-    _check(library("attention_generic").qf_attention_generic_ex(
+    _check(library("attention_generic").qf_attention_generic_masked(
         _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
         _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
-        _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _ptr(sinks), _I(int(bool(shared_values))), _stream()),
-        "attention_generic")
+        _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _ptr(sinks), _I(int(bool(shared_values))),
+        _I(int(chunk)), _F(softcap), _stream()), "attention_generic")
 
 
 FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
@@ -1289,3 +1307,202 @@ def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: 
     if code == 801:
         raise KernelError("tc_gemm_grouped: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
     _check(code, "tc_gemm_grouped")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Elementwise kernels of feed-forwards with a bias and of capped logits (csrc/activation.cu)
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], kind: str, out: torch.Tensor) -> None:
+    """out = act(x + bias), float32 inside. kind: relu2 (the square of relu), gelu_tanh, silu, relu."""
+    _dev("x", x)
+    _dev("out", out, x.dtype)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"bias_act: unknown activation {kind!r}; known: {', '.join(ACTIVATIONS)}")
+    rows, width = x.shape
+    if out.shape != x.shape:
+        raise KernelError("bias_act: out must have x's shape")
+    if bias is not None:
+        _dev("bias", bias, x.dtype)
+        if bias.numel() != width:
+            raise KernelError("bias_act: bias must hold one element per column")
+    _check(library("activation").qf_bias_act(_I(_is_bf16(x.dtype)), _ptr(x), _ptr(bias), _ptr(out), _I(rows), _I(width),
+                                             _I(ACTIVATIONS[kind]), _stream()), "bias_act")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; float32 (logits)."""
+    _dev("x", x, torch.float32)
+    if cap <= 0:
+        raise KernelError("softcap_: the cap must be positive")
+    _check(library("activation").qf_softcap(_ptr(x), _LL(x.numel()), _F(cap), _stream()), "softcap_")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Recurrent mixers (csrc/recurrent.cu): a state of fixed size per sequence, S <- decay * S + take * k v^T, y = S^T q.
+# `state` is a cache's fixed-size state of one schedule entry, float32 [slots, floats]; each kernel is told where in a
+# slot's row its piece starts. A sequence whose slot is -1 (padding) runs from a zero state and stores nothing.
+def _state(state: torch.Tensor, *pieces) -> None:
+    _dev("state", state, torch.float32)
+    if state.dim() != 2:
+        raise KernelError("the recurrent state must be float32 [slots, floats]")
+    for offset, size in pieces:
+        if offset < 0 or offset + size > state.shape[1]:
+            raise KernelError(f"a piece of {size} floats at {offset} does not fit a state of {state.shape[1]} floats per slot")
+
+
+def _rows(name: str, t: torch.Tensor, dtype=None) -> None:
+    _dev(name, t, dtype, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-d with unit inner stride")
+
+
+def stabilized_gates(pre: torch.Tensor, bias: torch.Tensor, cap: float, cu_q: torch.Tensor, slots: torch.Tensor,
+                     state: torch.Tensor, m_offset: int, n_heads: int, decay: torch.Tensor, take: torch.Tensor,
+                     floor: torch.Tensor) -> None:
+    """The exponential gates of a matrix memory with a running maximum, per head. pre: float32 [T, 2 H], the input gate's
+    and then the forget gate's pre-activations; bias float32 [2 H]. With a = cap tanh((pre_i + b_i) / cap),
+    f = logsigmoid(cap tanh((pre_f + b_f) / cap)) and m the running maximum kept in `state` (H floats at m_offset, 0 at a
+    sequence's start): m' = max(f + m, a), decay = exp(f + m - m'), take = exp(a - m'), floor = exp(-m'); all float32 [T, H]."""
+    _rows("pre", pre, torch.float32)
+    _dev("bias", bias, torch.float32)
+    n = pre.shape[0]
+    if pre.shape[1] != 2 * n_heads or bias.numel() != 2 * n_heads:
+        raise KernelError("stabilized_gates: pre must be [T, 2 * heads], bias [2 * heads]")
+    for name, t in (("decay", decay), ("take", take), ("floor", floor)):
+        _dev(name, t, torch.float32)
+        if t.shape != (n, n_heads):
+            raise KernelError(f"stabilized_gates: {name} must be float32 [T, heads]")
+    _state(state, (m_offset, n_heads))
+    _check(library("recurrent").qf_stabilized_gates(
+        _ptr(pre), _I(pre.stride(0)), _ptr(bias), _F(cap), _ptr(cu_q), _ptr(slots), _I(cu_q.numel() - 1), _ptr(state),
+        _LL(state.stride(0)), _LL(m_offset), _I(n_heads), _ptr(decay), _ptr(take), _ptr(floor), _stream()), "stabilized_gates")
+
+
+def decay_gates(dt_pre: torch.Tensor, dt_bias: torch.Tensor, rate_log: torch.Tensor, decay: torch.Tensor,
+                take: torch.Tensor) -> None:
+    """The gates of a state-space recurrence: dt = softplus(dt_pre + dt_bias), decay = exp(-exp(rate_log) * dt), take = dt.
+    dt_pre float32 [T, H] (rows may be strided); dt_bias, rate_log float32 [H]; decay, take float32 [T, H]."""
+    _rows("dt_pre", dt_pre, torch.float32)
+    n, h = dt_pre.shape
+    for name, t in (("dt_bias", dt_bias), ("rate_log", rate_log)):
+        _dev(name, t, torch.float32)
+        if t.numel() != h:
+            raise KernelError(f"decay_gates: {name} must hold one float32 per head")
+    for name, t in (("decay", decay), ("take", take)):
+        _dev(name, t, torch.float32)
+        if t.shape != (n, h):
+            raise KernelError(f"decay_gates: {name} must be float32 [T, heads]")
+    _check(library("recurrent").qf_decay_gates(_ptr(dt_pre), _I(dt_pre.stride(0)), _ptr(dt_bias), _ptr(rate_log), _I(n), _I(h),
+                                               _ptr(decay), _ptr(take), _stream()), "decay_gates")
+
+
+OUTER_STATE_MAX_DIM = 256
+
+
+def outer_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, take: torch.Tensor,
+                     cu_q: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, s_offset: int, n_offset: int,
+                     n_heads: int, n_groups: int, dim: int, vdim: int, q_scale: float, y: torch.Tensor,
+                     nq: Optional[torch.Tensor]) -> None:
+    """The recurrence of a matrix state per head, token after token of every sequence, all float32 inside:
+        S <- decay_t S + take_t k_t v_t^T   (S: dim x vdim, kept in `state` at s_offset as [heads, dim, vdim]);  y_t = S^T (q_scale q_t)
+    and, with `nq`, a vector n <- decay_t n + take_t k_t beside it (at n_offset, [heads, dim]) and nq_t = n . (q_scale q_t).
+    q, k: [T, groups * dim] (head h reads group h // (heads / groups)), v: [T, heads * vdim], in the activation dtype, rows
+    may be strided; decay, take: float32 [T, heads]; y: float32 [T, heads * vdim]; nq: float32 [T, heads] or None."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _rows(name, t, q.dtype)
+    _is_bf16(q.dtype)
+    n = q.shape[0]
+    if n_groups <= 0 or n_heads % n_groups or q.shape[1] != n_groups * dim or k.shape != q.shape or v.shape != (n, n_heads * vdim):
+        raise KernelError("outer_state_scan: q, k must be [T, groups * dim], v [T, heads * vdim]")
+    if dim > OUTER_STATE_MAX_DIM:
+        raise KernelError(f"outer_state_scan: a state of {dim} rows per head exceeds the kernel's {OUTER_STATE_MAX_DIM}")
+    for name, t in (("decay", decay), ("take", take)):
+        _dev(name, t, torch.float32)
+        if t.shape != (n, n_heads):
+            raise KernelError(f"outer_state_scan: {name} must be float32 [T, heads]")
+    _dev("y", y, torch.float32)
+    if y.shape != (n, n_heads * vdim):
+        raise KernelError("outer_state_scan: y must be float32 [T, heads * vdim]")
+    pieces = [(s_offset, n_heads * dim * vdim)]
+    if nq is not None:
+        _dev("nq", nq, torch.float32)
+        if nq.shape != (n, n_heads):
+            raise KernelError("outer_state_scan: nq must be float32 [T, heads]")
+        pieces.append((n_offset, n_heads * dim))
+    _state(state, *pieces)
+    _check(library("recurrent").qf_outer_state_scan(
+        _I(_is_bf16(q.dtype)), _ptr(q), _I(q.stride(0)), _ptr(k), _I(k.stride(0)), _ptr(v), _I(v.stride(0)), _ptr(decay),
+        _ptr(take), _ptr(cu_q), _ptr(slots), _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(s_offset),
+        _LL(n_offset if nq is not None else -1), _I(n_heads), _I(n_groups), _I(dim), _I(vdim), _F(q_scale), _ptr(y), _ptr(nq),
+        _stream()), "outer_state_scan")
+
+
+GATES = {"sigmoid": 0, "silu": 1}
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_parts: int,
+                     n_heads: int, gate_kind: str, gate_first: bool, nq: Optional[torch.Tensor] = None,
+                     floor: Optional[torch.Tensor] = None, floor_add: float = 0.0, skip: Optional[torch.Tensor] = None,
+                     skip_x: Optional[torch.Tensor] = None) -> None:
+    """What follows a recurrent mixer's scan, one pass per token, float32 inside. y: float32 [T, C] in `n_heads` heads.
+      with nq, floor (float32 [T, heads]):  y <- y / (max(|nq|, floor) + floor_add)          per head
+      with skip (float32 [heads]), skip_x [T, C]:  y <- y + skip[head] * skip_x              per head
+      gate_first:  y <- y * act(gate);   y <- y / rms(y) over each of `n_parts` equal parts (eps inside the root);
+      y <- y * weight;   not gate_first:  y <- y * act(gate).   act: sigmoid or silu.
+    gate, skip_x: [T, C] in the activation dtype, rows may be strided; weight [C] and out [T, C] in the activation dtype."""
+    _dev("y", y, torch.float32)
+    _rows("gate", gate, out.dtype)
+    _dev("weight", weight, out.dtype)
+    _dev("out", out)
+    _is_bf16(out.dtype)
+    n, c = y.shape
+    if gate.shape != (n, c) or out.shape != (n, c) or weight.numel() != c or n_parts <= 0 or c % n_parts or c % n_heads:
+        raise KernelError("gated_group_norm: gate and out must be [T, C] like y, weight [C]; parts and heads must divide C")
+    if gate_kind not in GATES:
+        raise KernelError(f"gated_group_norm: unknown gate {gate_kind!r}")
+    if (nq is None) != (floor is None) or (skip is None) != (skip_x is None):
+        raise KernelError("gated_group_norm: nq goes with floor, skip with skip_x")
+    if nq is not None:
+        for name, t in (("nq", nq), ("floor", floor)):
+            _dev(name, t, torch.float32)
+            if t.shape != (n, n_heads):
+                raise KernelError(f"gated_group_norm: {name} must be float32 [T, heads]")
+    if skip is not None:
+        _dev("skip", skip, torch.float32)
+        _rows("skip_x", skip_x, out.dtype)
+        if skip.numel() != n_heads or skip_x.shape != (n, c):
+            raise KernelError("gated_group_norm: skip must be float32 [heads], skip_x [T, C]")
+    _check(library("recurrent").qf_gated_group_norm(
+        _I(_is_bf16(out.dtype)), _ptr(y), _ptr(gate), _I(gate.stride(0)), _ptr(weight), _F(eps), _ptr(out), _I(n), _I(c),
+        _I(n_parts), _I(n_heads), _I(GATES[gate_kind]), _I(1 if gate_first else 0), _ptr(nq), _ptr(floor), _F(floor_add),
+        _ptr(skip), _ptr(skip_x), _I(skip_x.stride(0) if skip_x is not None else 0), _stream()), "gated_group_norm")
+
+
+CONV_MAX_TAPS = 16
+
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], cu_q: torch.Tensor,
+                     tok_seq: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, offset: int, out: torch.Tensor) -> None:
+    """A causal convolution per channel over each sequence's tokens, then silu: out[t, c] = silu(b[c] + sum_j w[c, j] *
+    x[t - (taps - 1 - j), c]); inputs before the step's first token come from `state` (the sequence's last taps - 1 inputs,
+    float32 [taps - 1, C] at `offset`, zeros at a sequence's start), which then takes the step's last taps - 1 inputs.
+    x: [T, C] in the activation dtype (rows may be strided); weight [C, taps], bias [C] float32; out [T, C]."""
+    _rows("x", x)
+    _dev("out", out, x.dtype)
+    _dev("weight", weight, torch.float32)
+    _is_bf16(x.dtype)
+    n, c = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != c or out.shape != (n, c) or not 1 <= taps <= CONV_MAX_TAPS:
+        raise KernelError(f"causal_conv_silu: weight must be [C, taps <= {CONV_MAX_TAPS}], out [T, C]")
+    if bias is not None:
+        _dev("bias", bias, torch.float32)
+        if bias.numel() != c:
+            raise KernelError("causal_conv_silu: bias must hold one float32 per channel")
+    _state(state, (offset, (taps - 1) * c))
+    _check(library("recurrent").qf_causal_conv_silu(
+        _I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _ptr(weight), _ptr(bias), _ptr(cu_q), _ptr(tok_seq), _ptr(slots),
+        _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(offset), _I(taps), _I(n), _I(c), _ptr(out), _stream()),
+        "causal_conv_silu")

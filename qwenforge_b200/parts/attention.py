@@ -10,6 +10,16 @@
 Nothing here is specific to one model: head counts, head size, biases, scale, window and the
 position part all come from the spec. A step's queries attend to the cache only, which already
 holds the step's own keys: whole prompts, continuations and single tokens are the same code.
+
+Options that other designs switch on, each a parameter of the spec (all off for the plain form above):
+  value_dim      values of another size than keys. The smaller of the two is padded with zeros up to the larger in the
+                 projection weights, once at load time, so that the cache and the kernels see one head size; zeros add
+                 nothing to a score and come out as zeros.
+  unit_norm_eps  after the rotation, q and k are divided by their root mean square per head (no weight)
+  softcap        score <- softcap * tanh(score / softcap), after the scale
+  chunk          key j is visible to query i only inside i's block of `chunk` positions (counted from position 0)
+  sink           "unit": one more term exp(0) in the softmax's denominator, with no value
+  own_kv         false: no key and value projections; the layer reads the cache of the schedule entry it is pointed at
 """
 from __future__ import annotations
 
@@ -30,7 +40,8 @@ TC_PREFILL_MIN_TOKENS = {64: 1024, 128: 512}
 
 
 class GqaAttention(Mixer):
-    """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, out_bias, scale, window, position (PartSpec | None).
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, out_bias, scale, window, position (PartSpec | None),
+    and optionally value_dim, unit_norm_eps, softcap, chunk, sink, own_kv (see the top of the file).
     tensors: q_weight, k_weight, v_weight, o_weight (+ q_bias, k_bias, v_bias, o_bias when enabled)."""
 
     def __init__(self, spec):
@@ -39,10 +50,22 @@ class GqaAttention(Mixer):
         self.hidden = int(p["hidden_size"])
         self.n_heads = int(p["num_heads"])
         self.n_kv = int(p["num_kv_heads"])
-        self.head_dim = int(p["head_dim"])
+        self.key_dim = int(p["head_dim"])
+        self.value_dim = int(p.get("value_dim") or self.key_dim)
+        self.head_dim = max(self.key_dim, self.value_dim)   # what the cache and the kernels see
+        self.unit_norm_eps = None if p.get("unit_norm_eps") is None else float(p["unit_norm_eps"])
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.chunk = int(p.get("chunk") or 0)
+        self.sink = str(p.get("sink") or "none")
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.sink not in ("none", "unit"):
+            raise ValueError(f"gqa_attention: sink {self.sink!r} is not known ('none' or 'unit')")
+        # the form that every tensor-core kernel and fused product of this part takes
+        self.plain = (self.value_dim == self.key_dim and self.unit_norm_eps is None and self.softcap == 0.0 and self.chunk == 0
+                      and self.sink == "none" and self.own_kv)
         self.qkv_bias = bool(p.get("qkv_bias", False))
         self.out_bias = bool(p.get("out_bias", False))
-        self.scale = float(p.get("scale") or self.head_dim ** -0.5)
+        self.scale = float(p.get("scale") or self.key_dim ** -0.5)
         self.window = int(p.get("window") or 0)
         if self.n_heads % self.n_kv:
             raise ValueError(f"gqa_attention: {self.n_heads} heads are not divisible by {self.n_kv} kv heads")
@@ -51,24 +74,23 @@ class GqaAttention(Mixer):
         self.position = build_part("position", p["position"]) if p.get("position") is not None else None
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv * self.head_dim
-        self.qkv_weight = self.qkv_bias_t = self.o_weight = self.o_bias_t = None
+        self.qkv_weight = self.qkv_bias_t = self.o_weight = self.o_bias_t = self.sinks = None
 
     def sub_parts(self):
         return [self.position] if self.position is not None else []
 
     def tensor_specs(self):
-        specs = [
-            TensorSpec(self.file_name("q_weight"), (self.q_width, self.hidden)),
-            TensorSpec(self.file_name("k_weight"), (self.kv_width, self.hidden)),
-            TensorSpec(self.file_name("v_weight"), (self.kv_width, self.hidden)),
-            TensorSpec(self.file_name("o_weight"), (self.hidden, self.q_width)),
-        ]
+        kd, vd = self.key_dim, self.value_dim
+        specs = [TensorSpec(self.file_name("q_weight"), (self.n_heads * kd, self.hidden)),
+                 TensorSpec(self.file_name("o_weight"), (self.hidden, self.n_heads * vd))]
+        if self.own_kv:
+            specs += [TensorSpec(self.file_name("k_weight"), (self.n_kv * kd, self.hidden)),
+                      TensorSpec(self.file_name("v_weight"), (self.n_kv * vd, self.hidden))]
         if self.qkv_bias:
-            specs += [
-                TensorSpec(self.file_name("q_bias"), (self.q_width,), init="bias"),
-                TensorSpec(self.file_name("k_bias"), (self.kv_width,), init="bias"),
-                TensorSpec(self.file_name("v_bias"), (self.kv_width,), init="bias"),
-            ]
+            specs.append(TensorSpec(self.file_name("q_bias"), (self.n_heads * kd,), init="bias"))
+            if self.own_kv:
+                specs += [TensorSpec(self.file_name("k_bias"), (self.n_kv * kd,), init="bias"),
+                          TensorSpec(self.file_name("v_bias"), (self.n_kv * vd,), init="bias")]
         if self.out_bias:
             specs.append(TensorSpec(self.file_name("o_bias"), (self.hidden,), init="bias"))
         return specs
@@ -77,29 +99,51 @@ class GqaAttention(Mixer):
         libs = {"rope_cache", "attention_generic"}
         if dtype == torch.float32:
             libs.add("gemm_f32")
-        elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
+        elif self.plain and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
             libs |= {"attention_decode", "attention_prefill", "skinny_gemm", "wide_gemm", "fold_project"}
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 libs.add("attention_prefill_tc")
         return libs
 
     def cache_need(self):
-        return KvNeed(self.n_kv, self.head_dim, self.window)
+        return KvNeed(self.n_kv, self.head_dim, self.window, chunk=self.chunk)
+
+    def _padded(self, rows: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """Rows [heads * size, ...] of a projection (or its bias) with every head filled up with zero rows to head_dim."""
+        if size == self.head_dim:
+            return rows
+        wide = rows.new_zeros((heads, self.head_dim) + tuple(rows.shape[1:]))
+        wide[:, :size] = rows.view((heads, size) + tuple(rows.shape[1:]))
+        return wide.view((heads * self.head_dim,) + tuple(rows.shape[1:]))
 
     def bind(self, tensors, dtype, device):
         t = lambda logical: tensors[self.file_name(logical)]
-        self.qkv_weight = torch.cat((t("q_weight"), t("k_weight"), t("v_weight")), dim=0).contiguous()
+        kd, vd = self.key_dim, self.value_dim
+        pieces = [self._padded(t("q_weight"), self.n_heads, kd)]
+        if self.own_kv:
+            pieces += [self._padded(t("k_weight"), self.n_kv, kd), self._padded(t("v_weight"), self.n_kv, vd)]
+        self.qkv_weight = torch.cat(pieces, dim=0).contiguous()
         if self.qkv_bias:
-            self.qkv_bias_t = torch.cat((t("q_bias"), t("k_bias"), t("v_bias")), dim=0).contiguous()
-        self.o_weight = t("o_weight")
+            pieces = [self._padded(t("q_bias"), self.n_heads, kd)]
+            if self.own_kv:
+                pieces += [self._padded(t("k_bias"), self.n_kv, kd), self._padded(t("v_bias"), self.n_kv, vd)]
+            self.qkv_bias_t = torch.cat(pieces, dim=0).contiguous()
+        o = t("o_weight")
+        if vd != self.head_dim:   # columns of zeros under the attended heads' padding
+            o = self._padded(o.t().contiguous(), self.n_heads, vd).t().contiguous()
+        self.o_weight = o
         if self.out_bias:
             self.o_bias_t = t("o_bias")
+        if self.sink == "unit":
+            self.sinks = torch.zeros(self.n_heads, dtype=torch.float32, device=device)
 
     def step_weights(self):
         return [t for t in (self.qkv_weight, self.qkv_bias_t, self.o_weight, self.o_bias_t) if t is not None]
 
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
+        if not self.plain:
+            return self._forward_with_options(x, ctx, site, writes_cache)
         fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16
                 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS)
         plan = self.decode_plan(ctx) if fast and ctx.is_decode else None
@@ -136,6 +180,27 @@ class GqaAttention(Mixer):
                                   max_kv_len=ctx.max_kv_len)
         return ops.linear(attended, self.o_weight, self.o_bias_t)
 
+    def _forward_with_options(self, x, ctx, site, writes_cache):
+        """The step with any of the options on: one product for what the layer projects, one kernel for bias, rotation,
+        unit norm and the cache write, then attention over the cache with the mask, the cap and the sink."""
+        n = x.shape[0]
+        if self.position is not None and self.position.fused_rotary() is None:
+            raise ValueError("gqa_attention: the options need a position part with a fused form (or none)")
+        if not self.own_kv and writes_cache:
+            raise ValueError("gqa_attention: a layer without keys and values of its own must be pointed at another entry's cache")
+        inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
+        qkv = ops.linear_rows(x, self.qkv_weight)
+        q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+        args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
+        ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args, writes_cache,
+                             ctx.err, bias=self.qkv_bias_t, unit_norm_eps=self.unit_norm_eps, norm_dim=self.key_dim,
+                             has_kv=self.own_kv)
+        attended = torch.empty_like(q)
+        ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
+                              self.scale, self.window, ctx.err, scratch=ctx.decode_scratch, max_kv_len=ctx.max_kv_len,
+                              sinks=self.sinks, chunk=self.chunk, softcap=self.softcap)
+        return ops.linear(attended, self.o_weight, self.o_bias_t) if self.o_bias_t is not None else ops.linear_rows(attended, self.o_weight)
+
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,
     # rotation and cache write ride on the QKV product and the addition on the output projection wherever a kernel of
     # this library takes the sizes and is the faster way by measurement; each product chooses for itself.
@@ -150,8 +215,8 @@ class GqaAttention(Mixer):
         return qkv, ops.residual_product_way(rows, self.o_weight)
 
     def fused_takes(self, ctx) -> bool:
-        if not (ctx.attention == "auto" and ctx.is_decode and ctx.dtype == torch.bfloat16 and ctx.n_tokens <= ops.WIDE_MAX_ROWS
-                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.out_bias):
+        if not (self.plain and ctx.attention == "auto" and ctx.is_decode and ctx.dtype == torch.bfloat16
+                and ctx.n_tokens <= ops.WIDE_MAX_ROWS and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.out_bias):
             return False
         rotary = self.position.fused_rotary() if self.position is not None else None
         if self.position is not None and (rotary is None or rotary[1] != self.head_dim):

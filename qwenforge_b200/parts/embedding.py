@@ -67,12 +67,14 @@ class TokenPositionEmbedding(Embedding):
 class LinearHead(Part):
     """params: vocab_size, width, tied. tensors: weight [vocab_size, width] (the embedding's tensor when tied), and
     optionally weight_fallback: the tensor that serves when the files hold no `weight` (the reference takes the
-    embedding table whenever lm_head.weight is absent, student_engine.py:359). Returns float32 logits in both precisions."""
+    embedding table whenever lm_head.weight is absent, student_engine.py:359). Returns float32 logits in both precisions.
+    Optional param softcap > 0: logits <- softcap * tanh(logits / softcap)."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(self.params["vocab_size"])
         self.width = int(self.params["width"])
+        self.softcap = float(self.params.get("softcap") or 0.0)
         self.weight = None
 
     def tensor_specs(self):
@@ -80,7 +82,7 @@ class LinearHead(Part):
                            fallback=self.spec.tensors.get("weight_fallback"))]
 
     def kernel_libraries(self, dtype):
-        return {"gemm_f32"} if dtype == torch.float32 else set()
+        return ({"gemm_f32"} if dtype == torch.float32 else set()) | ({"activation"} if self.softcap > 0 else set())
 
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.file_name("weight")]
@@ -89,7 +91,10 @@ class LinearHead(Part):
         return [self.weight]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        if self.softcap > 0:
+            ops.softcap_(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

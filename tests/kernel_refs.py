@@ -70,15 +70,19 @@ def _kv_rows(site, slot, positions, head, which):
     return pages, offs
 
 
-def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, site, write_cache, err, bias=None):
+def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, site, write_cache, err, bias=None,
+                     unit_norm_eps=None, norm_dim=0, has_kv=True):
     n = qkv.shape[0]
     d, kvh = site.head_dim, site.kv_heads
     x = _f(qkv)
     if bias is not None:
         x = x + _f(bias)
     q = x[:, :n_heads * d].reshape(n, n_heads, d).clone()
-    k = x[:, n_heads * d:(n_heads + kvh) * d].reshape(n, kvh, d).clone()
-    v = x[:, (n_heads + kvh) * d:].reshape(n, kvh, d)
+    if has_kv:
+        k = x[:, n_heads * d:(n_heads + kvh) * d].reshape(n, kvh, d).clone()
+        v = x[:, (n_heads + kvh) * d:].reshape(n, kvh, d)
+    else:
+        k, v = q[:, :0].clone(), None
     if inv_freq is not None and rot_dim > 0:
         angle = (tok_pos.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32)).to(torch.float64)
         cos, sin = angle.cos().unsqueeze(1), angle.sin().unsqueeze(1)
@@ -87,6 +91,10 @@ def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q
             x1, x2 = t[..., :half].clone(), t[..., half:rot_dim].clone()
             t[..., :half] = x1 * cos - x2 * sin
             t[..., half:rot_dim] = x2 * cos + x1 * sin
+    if unit_norm_eps is not None:
+        over = norm_dim or d
+        for t in (q, k):
+            t /= torch.sqrt(t[..., :over].square().mean(-1, keepdim=True) + unit_norm_eps)
     q_out.copy_(q.reshape(n, n_heads * d).to(q_out.dtype))
     if not write_cache:
         return
@@ -120,7 +128,7 @@ def gather_keys(site, slot, lo, hi):
 
 
 def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, scratch=None, max_kv_len=None,
-                      sinks=None, shared_values=False):
+                      sinks=None, shared_values=False, chunk=0, softcap=0.0):
     d, kvh = site.head_dim, site.kv_heads
     groups = n_heads // kvh
     for s in range(n_seqs):
@@ -132,6 +140,8 @@ def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q
         for t in range(b, e):
             p = int(tok_pos[t])
             lo = max(0, p - window + 1) if window > 0 else 0
+            if chunk > 0:
+                lo = max(lo, p // chunk * chunk)
             if shared_values:
                 k = v = gather_keys(site, slot, lo, p + 1)
             else:
@@ -140,6 +150,8 @@ def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q
             k = k.repeat_interleave(groups, dim=0)
             v = v.repeat_interleave(groups, dim=0)
             scores = torch.einsum("hd,hjd->hj", qt, k) * scale
+            if softcap > 0:
+                scores = softcap * torch.tanh(scores / softcap)
             if sinks is not None:   # one more term in the denominator, with no value
                 weights = torch.softmax(torch.cat((scores, _f(sinks)[:, None]), dim=-1), -1)[:, :-1]
             else:
@@ -281,7 +293,113 @@ def expert_linear(x, weight, plan, out, gather=False):
     out.copy_(torch.einsum("rk,rnk->rn", rows, _f(weight)[plan.row_expert]).to(out.dtype))
 
 
-ALL = dict(expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
+def bias_act(x, bias, kind, out):
+    z = _f(x) if bias is None else _f(x) + _f(bias)
+    if kind == "relu2":
+        y = torch.relu(z) ** 2
+    elif kind == "gelu_tanh":
+        y = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    elif kind == "silu":
+        y = z * torch.sigmoid(z)
+    else:
+        y = torch.relu(z)
+    out.copy_(y.to(out.dtype))
+
+
+def softcap_(x, cap):
+    x.copy_((cap * torch.tanh(_f(x) / cap)).to(x.dtype))
+
+
+def stabilized_gates(pre, bias, cap, cu_q, slots, state, m_offset, n_heads, decay, take, floor):
+    z = _f(pre) + _f(bias)
+    a = cap * torch.tanh(z[:, :n_heads] / cap)
+    f = torch.nn.functional.logsigmoid(cap * torch.tanh(z[:, n_heads:] / cap))
+    for s in range(cu_q.numel() - 1):
+        slot = int(slots[s])
+        m = _f(state[slot, m_offset:m_offset + n_heads]) if slot >= 0 else torch.zeros(n_heads, dtype=torch.float64)
+        for t in range(int(cu_q[s]), int(cu_q[s + 1])):
+            m_new = torch.maximum(f[t] + m, a[t])
+            decay[t] = torch.exp(f[t] + m - m_new).float()
+            take[t] = torch.exp(a[t] - m_new).float()
+            floor[t] = torch.exp(-m_new).float()
+            m = m_new
+        if slot >= 0:
+            state[slot, m_offset:m_offset + n_heads] = m.float()
+
+
+def decay_gates(dt_pre, dt_bias, rate_log, decay, take):
+    dt = torch.nn.functional.softplus(_f(dt_pre) + _f(dt_bias))
+    decay.copy_(torch.exp(-torch.exp(_f(rate_log)) * dt).float())
+    take.copy_(dt.float())
+
+
+def outer_state_scan(q, k, v, decay, take, cu_q, slots, state, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq):
+    per = n_heads // n_groups
+    for s in range(cu_q.numel() - 1):
+        slot = int(slots[s])
+        S = torch.zeros(n_heads, dim, vdim, dtype=torch.float64)
+        nv = torch.zeros(n_heads, dim, dtype=torch.float64)
+        if slot >= 0:
+            S = _f(state[slot, s_offset:s_offset + n_heads * dim * vdim]).view(n_heads, dim, vdim).clone()
+            if nq is not None:
+                nv = _f(state[slot, n_offset:n_offset + n_heads * dim]).view(n_heads, dim).clone()
+        for t in range(int(cu_q[s]), int(cu_q[s + 1])):
+            qt = (_f(q[t]) * q_scale).view(n_groups, dim).repeat_interleave(per, dim=0)
+            kt = _f(k[t]).view(n_groups, dim).repeat_interleave(per, dim=0)
+            vt = _f(v[t]).view(n_heads, vdim)
+            d, g = _f(decay[t])[:, None], _f(take[t])[:, None]
+            S = d[:, :, None] * S + g[:, :, None] * kt[:, :, None] * vt[:, None, :]
+            y[t] = torch.einsum("hdv,hd->hv", S, qt).reshape(-1).float()
+            if nq is not None:
+                nv = d * nv + g * kt
+                nq[t] = (nv * qt).sum(-1).float()
+        if slot >= 0:
+            state[slot, s_offset:s_offset + n_heads * dim * vdim] = S.reshape(-1).float()
+            if nq is not None:
+                state[slot, n_offset:n_offset + n_heads * dim] = nv.reshape(-1).float()
+
+
+def gated_group_norm(y, gate, weight, eps, out, n_parts, n_heads, gate_kind, gate_first, nq=None, floor=None, floor_add=0.0,
+                     skip=None, skip_x=None):
+    n, c = y.shape
+    z = _f(y).view(n, n_heads, c // n_heads)
+    if nq is not None:
+        z = z / (torch.maximum(_f(nq).abs(), _f(floor)) + floor_add)[:, :, None]
+    if skip is not None:
+        z = z + _f(skip)[None, :, None] * _f(skip_x).view(n, n_heads, -1)
+    z = z.reshape(n, c)
+    g = _f(gate)
+    g = torch.sigmoid(g) if gate_kind == "sigmoid" else g * torch.sigmoid(g)
+    if gate_first:
+        z = z * g
+    z = z.view(n, n_parts, c // n_parts)
+    z = (z / torch.sqrt(z.square().mean(-1, keepdim=True) + eps)).reshape(n, c) * _f(weight)
+    if not gate_first:
+        z = z * g
+    out.copy_(z.to(out.dtype))
+
+
+def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
+    n, c = x.shape
+    taps = weight.shape[1]
+    for s in range(cu_q.numel() - 1):
+        b, e = int(cu_q[s]), int(cu_q[s + 1])
+        slot = int(slots[s])
+        before = torch.zeros(taps - 1, c, dtype=torch.float64)
+        if slot >= 0:
+            before = _f(state[slot, offset:offset + (taps - 1) * c]).view(taps - 1, c)
+        padded = torch.cat((before, _f(x[b:e])))
+        z = sum(padded[j:j + e - b] * _f(weight)[:, j] for j in range(taps))
+        if bias is not None:
+            z = z + _f(bias)
+        out[b:e] = (z * torch.sigmoid(z)).to(out.dtype)
+        if slot >= 0:
+            state[slot, offset:offset + (taps - 1) * c] = padded[padded.shape[0] - (taps - 1):].reshape(-1).float()
+
+
+ALL = dict(bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,
+           outer_state_scan=outer_state_scan, gated_group_norm=gated_group_norm, causal_conv_silu=causal_conv_silu,
+           expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
            head_linear=head_linear, moe_plan=moe_plan, moe_gather=moe_gather, moe_combine=moe_combine, expert_linear=expert_linear,
            embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
            linear=linear, rope_cache_write=rope_cache_write, attention_generic=attention_generic, swiglu=swiglu,
