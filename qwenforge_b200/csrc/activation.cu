@@ -131,3 +131,80 @@ QF_EXPORT int qf_scaled_swiglu(int is_bf16, const void* gu, const float* row_sca
         return (int)launch_pdl(scaled_swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, row_scale, (bf16*)out, inter, total);
     return (int)launch_pdl(scaled_swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, row_scale, (float*)out, inter, total);
 }
+
+// out = act(x + bias): the first half of a feed-forward without a gate. kind 0: the square of relu, 1: tanh-GELU,
+// 2: silu, 3: relu. Float32 inside; bias may be null.
+__device__ __forceinline__ float activate(float z, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(z, 0.f);
+        return r * r;
+    }
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 2) return z / (1.f + expf(-z));
+    return fmaxf(z, 0.f);
+}
+
+template <typename T>
+__global__ void bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ out, int width, size_t total,
+                                int kind) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = Num<T>::to_f(x[i]) + (bias ? Num<T>::to_f(bias[i % width]) : 0.f);
+        out[i] = Num<T>::from_f(activate(z, kind));
+    }
+}
+
+// Eight bf16 elements per thread; needs width % 8 == 0 and 16-byte aligned pointers.
+__global__ void bias_act_bf16x8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bias, bf16* __restrict__ out, int width,
+                                       size_t total8, int kind) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 x4 = *reinterpret_cast<const uint4*>(x + i * 8);
+        uint4 b4 = make_uint4(0u, 0u, 0u, 0u);
+        if (bias) b4 = *reinterpret_cast<const uint4*>(bias + (i * 8) % width);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x4);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(x2[j]), b = __bfloat1622float2(b2[j]);
+            o2[j] = __floats2bfloat162_rn(activate(v.x + b.x, kind), activate(v.y + b.y, kind));
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = o4;
+    }
+}
+
+QF_EXPORT int qf_bias_act(int is_bf16, const void* x, const void* bias, void* out, int rows, int width, int kind,
+                          cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    if (total == 0) return 0;
+    if (kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    if (is_bf16 && width % 8 == 0 && ((uintptr_t)x | (uintptr_t)out | (uintptr_t)bias) % 16 == 0) {
+        const size_t total8 = total / 8;
+        const int b8 = (int)((total8 + 255) / 256 < most ? (total8 + 255) / 256 : most);
+        return (int)launch_pdl(bias_act_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)x, (const bf16*)bias, (bf16*)out,
+                               width, total8, kind);
+    }
+    if (is_bf16)
+        return (int)launch_pdl(bias_act_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (const bf16*)bias, (bf16*)out,
+                               width, total, kind);
+    return (int)launch_pdl(bias_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (const float*)bias, (float*)out,
+                           width, total, kind);
+}
+
+// x <- cap * tanh(x / cap) in place, float32 (logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+QF_EXPORT int qf_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const size_t want = ((size_t)total + 255) / 256;
+    return (int)launch_pdl(softcap_kernel, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, x, (size_t)total, cap);
+}

@@ -10,7 +10,9 @@
 // order of every row's arithmetic depends only on that row's own position and window: results
 // are bitwise independent of what else is in the batch and of how the tokens were cut into steps.
 //
-// Query i at position p sees keys j with max(0, p - window + 1) <= j <= p (window 0: all j <= p).
+// Query i at position p sees keys j with max(0, p - window + 1) <= j <= p (window 0: all j <= p); with `chunk` > 0 also
+// only the keys of its own block of `chunk` positions, j >= floor(p / chunk) * chunk (blocks counted from position 0 of
+// the sequence). `softcap` > 0: a score s, after the scale, becomes softcap * tanh(s / softcap).
 //
 // Two options that other kinds of attention need. `sinks` (float32, one per query head, or null): a learned logit that
 // joins the softmax's denominator once, unscaled, with no key and no value. `shared_values`: the values are the keys
@@ -34,12 +36,20 @@
 #define MAX_DPL_WIDE 16
 #define GEN_CHUNK 256       // keys per block of the split form; a multiple of KT
 
+// Lowest position that a query at `pos` sees.
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+
 template <typename T, bool SPLIT, int MAX_DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int* __restrict__ cu_q,
                          const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<T> site, int n_heads,
                          int group_chunk, int tokens_per_tile, float scale, int window, float* __restrict__ part_o,
-                         float* __restrict__ part_ml, int* err, const float* __restrict__ sinks, int shared_values) {
+                         float* __restrict__ part_ml, int* err, const float* __restrict__ sinks, int shared_values, int mask_block,
+                         float softcap) {
     extern __shared__ float smem[];
     const int D = site.head_dim, G = n_heads / site.kv_heads;
     const int chunks = (G + group_chunk - 1) / group_chunk;
@@ -79,7 +89,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
     // positions of the tile's tokens are consecutive: first_pos .. first_pos + n_tok - 1
     const int first_pos = tok_pos[q_begin + tile_tok0];
     const int last_pos = first_pos + n_tok - 1;
-    const int lo_min = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int lo_min = first_visible(first_pos, window, mask_block);   // rises with the position: the tile's lowest
 
     float m[ROWS_PER_WARP], l[ROWS_PER_WARP], acc[ROWS_PER_WARP][MAX_DPL];
     int row_pos[ROWS_PER_WARP], row_lo[ROWS_PER_WARP];
@@ -91,7 +101,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
         for (int dd = 0; dd < MAX_DPL; ++dd) acc[i][dd] = 0.f;
         const int r = warp + i * WARPS;
         row_pos[i] = r < n_rows ? first_pos + r / n_g : -1;
-        row_lo[i] = window > 0 ? max(0, row_pos[i] - window + 1) : 0;
+        row_lo[i] = row_pos[i] >= 0 ? first_visible(row_pos[i], window, mask_block) : 0;
     }
     const int dpl = (D + 31) / 32;
 
@@ -132,6 +142,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
             float s = 0.f;
             for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
             s *= scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             const bool visible = kj <= row_pos[i] && kj >= row_lo[i];
             s = visible ? s : -FLT_MAX;
             const float m_new = fmaxf(m[i], warp_max(s));
@@ -189,14 +200,14 @@ template <typename T>
 __global__ void attention_generic_fold_kernel(T* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                                               const int* __restrict__ slots, int n_heads, int D, int n_chunks, int window,
                                               const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              const float* __restrict__ sinks) {
+                                              const float* __restrict__ sinks, int chunk) {
     const int h = blockIdx.x, seq = blockIdx.y, t = cu_q[seq];
     T* o = out + ((size_t)t * n_heads + h) * D;
     if (slots[seq] < 0) {
         for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = Num<T>::from_f(0.f);
         return;
     }
-    const int pos = tok_pos[t], lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int pos = tok_pos[t], lo = first_visible(pos, window, chunk);
     const size_t row = ((size_t)seq * n_heads + h) * n_chunks;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float m = -FLT_MAX, l = 0.f, a = 0.f;
@@ -222,7 +233,7 @@ template <typename T, int MAX_DPL>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads,
                   int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks, int shared_values,
-                  cudaStream_t stream) {
+                  int chunk, float softcap, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (head_dim > 32 * MAX_DPL || kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     const int G = n_heads / kv_heads;
@@ -238,7 +249,7 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, kv_heads * chunks, n_seqs);
     attention_generic_kernel<T, false, MAX_DPL><<<grid, WARPS * 32, smem, stream>>>(
         (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, tokens_per_tile, scale, window, nullptr, nullptr,
-        err, sinks, shared_values);
+        err, sinks, shared_values, chunk, softcap);
     return (int)cudaGetLastError();
 }
 
@@ -246,7 +257,7 @@ template <typename T, int MAX_DPL>
 static int launch_decode(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                          const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads,
                          int n_seqs, int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
-                         const float* sinks, int shared_values, cudaStream_t stream) {
+                         const float* sinks, int shared_values, int chunk, float softcap, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (head_dim > 32 * MAX_DPL || kv_heads <= 0 || n_heads % kv_heads || max_kv_len <= 0) return (int)cudaErrorInvalidValue;
     const int G = n_heads / kv_heads;
@@ -260,11 +271,11 @@ static int launch_decode(const void* q, void* out, const int* cu_q, const int* t
     KvSite<T> site{(T*)base, table, page_elems, table_stride, kv_heads, head_dim};
     attention_generic_kernel<T, true, MAX_DPL><<<dim3(n_chunks, kv_heads * chunks, n_seqs), WARPS * 32, smem, stream>>>(
         (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, 1, scale, window, part_o, part_ml, err, nullptr,
-        shared_values);
+        shared_values, chunk, softcap);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     attention_generic_fold_kernel<T><<<dim3(n_heads, n_seqs), 64, 0, stream>>>((T*)out, cu_q, tok_pos, slots, n_heads, head_dim,
-                                                                               n_chunks, window, part_o, part_ml, sinks);
+                                                                               n_chunks, window, part_o, part_ml, sinks, chunk);
     return (int)cudaGetLastError();
 }
 
@@ -276,13 +287,23 @@ static int launch_decode(const void* q, void* out, const int* cu_q, const int* t
         return is_bf16 ? FN<bf16, MAX_DPL_SMALL>(__VA_ARGS__) : FN<float, MAX_DPL_SMALL>(__VA_ARGS__); \
     return is_bf16 ? FN<bf16, MAX_DPL_WIDE>(__VA_ARGS__) : FN<float, MAX_DPL_WIDE>(__VA_ARGS__);
 
+// chunk: > 0 limits a query to the keys of its own block of that many positions; softcap: > 0 caps the scores.
+QF_EXPORT int qf_attention_generic_masked(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                          const int* slots, void* base, const int* table, long long page_elems,
+                                          int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                          int max_q_len, float scale, int window, int* err, const float* sinks,
+                                          int shared_values, int chunk, float softcap, cudaStream_t stream) {
+    QF_GENERIC_DISPATCH(launch, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                        n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, chunk, softcap, stream)
+}
+
 QF_EXPORT int qf_attention_generic_ex(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
                                       const int* slots, void* base, const int* table, long long page_elems,
                                       int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                                       int max_q_len, float scale, int window, int* err, const float* sinks,
                                       int shared_values, cudaStream_t stream) {
-    QF_GENERIC_DISPATCH(launch, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
-                        n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream)
+    return qf_attention_generic_masked(is_bf16, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
+                                       head_dim, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, 0, 0.f, stream);
 }
 
 QF_EXPORT int qf_attention_generic(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
@@ -296,13 +317,24 @@ QF_EXPORT int qf_attention_generic(int is_bf16, const void* q, void* out, const 
 // The same for a step of ONE token per sequence, cut into chunks of keys (see the top of the file). `max_kv_len`: an
 // upper bound of any sequence's length after the step; scratch: part_o float32 [n_seqs * n_heads * n_chunks * head_dim],
 // part_ml float32 [n_seqs * n_heads * n_chunks * 2] with n_chunks = ceil(max_kv_len / 256).
+QF_EXPORT int qf_attention_generic_decode_masked(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                                 const int* slots, void* base, const int* table, long long page_elems,
+                                                 int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                                 int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
+                                                 const float* sinks, int shared_values, int chunk, float softcap,
+                                                 cudaStream_t stream) {
+    QF_GENERIC_DISPATCH(launch_decode, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                        n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err, sinks, shared_values, chunk, softcap, stream)
+}
+
 QF_EXPORT int qf_attention_generic_decode_ex(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
                                              const int* slots, void* base, const int* table, long long page_elems,
                                              int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                                              int max_kv_len, float scale, int window, float* part_o, float* part_ml, int* err,
                                              const float* sinks, int shared_values, cudaStream_t stream) {
-    QF_GENERIC_DISPATCH(launch_decode, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
-                        n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err, sinks, shared_values, stream)
+    return qf_attention_generic_decode_masked(is_bf16, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride,
+                                              kv_heads, head_dim, n_heads, n_seqs, max_kv_len, scale, window, part_o, part_ml, err,
+                                              sinks, shared_values, 0, 0.f, stream);
 }
 
 QF_EXPORT int qf_attention_generic_decode(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,

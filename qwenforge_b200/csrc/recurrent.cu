@@ -1,0 +1,337 @@
+// Kernels of the recurrent mixers: a state of fixed size per sequence instead of keys and values per position.
+//
+//   S <- decay_t S + take_t k_t v_t^T,   y_t = S^T q_t        per head; S is dim x vdim, float32, kept per sequence
+//
+// A state row of a sequence is `state + slot * slot_stride`; every kernel is told at which float of the row its piece
+// starts. A sequence whose slot is -1 (a padding entry of the batch) runs from a zero state and stores nothing.
+// Everything is float32 inside; q, k, v, the gate of the output and the convolution's input and output carry the
+// activation dtype. A token's result depends on its own sequence only, and on the tokens before it in their order, never
+// on how they were cut into steps: every kernel walks a sequence token by token in one fixed order of operations.
+#include <float.h>
+
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------------------------
+// Exponential gates with a running maximum (the mLSTM's): one warp per (sequence, head). The lanes take 32 tokens at a
+// time: each works out its token's two log gates (tanh, logsigmoid), then the maximum runs through the 32 in order,
+// then each lane forms its token's three exponentials.
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__global__ void __launch_bounds__(128)
+stabilized_gates_kernel(const float* __restrict__ pre, int pre_stride, const float* __restrict__ bias, float cap,
+                        const int* __restrict__ cu_q, const int* __restrict__ slots, int n_seqs, float* __restrict__ state,
+                        long long slot_stride, long long m_offset, int n_heads, float* __restrict__ decay,
+                        float* __restrict__ take, float* __restrict__ floor_out) {
+    grid_chain_entry();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= n_seqs * n_heads) return;
+    const int seq = item / n_heads, head = item % n_heads;
+    const int begin = cu_q[seq], end = cu_q[seq + 1], slot = slots[seq];
+    float* m_ptr = slot >= 0 ? state + slot * slot_stride + m_offset + head : nullptr;
+    float m = m_ptr ? *m_ptr : 0.f;
+    const float bi = bias[head], bf = bias[n_heads + head];
+    for (int t0 = begin; t0 < end; t0 += 32) {
+        const int t = t0 + lane;
+        float a = 0.f, f = 0.f;
+        if (t < end) {
+            a = cap * tanhf((pre[(size_t)t * pre_stride + head] + bi) / cap);
+            f = log_sigmoid(cap * tanhf((pre[(size_t)t * pre_stride + n_heads + head] + bf) / cap));
+        }
+        float m_before = 0.f, m_mine = 0.f;
+        const int n_here = min(32, end - t0);
+        for (int j = 0; j < n_here; ++j) {   // the same additions in the same order for every cut of the sequence
+            const float aj = __shfl_sync(0xffffffffu, a, j), fj = __shfl_sync(0xffffffffu, f, j);
+            const float m_new = fmaxf(fj + m, aj);
+            if (lane == j) {
+                m_before = m;
+                m_mine = m_new;
+            }
+            m = m_new;
+        }
+        if (t < end) {
+            decay[(size_t)t * n_heads + head] = expf(f + m_before - m_mine);
+            take[(size_t)t * n_heads + head] = expf(a - m_mine);
+            floor_out[(size_t)t * n_heads + head] = expf(-m_mine);
+        }
+    }
+    if (m_ptr && lane == 0) *m_ptr = m;
+}
+
+QF_EXPORT int qf_stabilized_gates(const float* pre, int pre_stride, const float* bias, float cap, const int* cu_q,
+                                  const int* slots, int n_seqs, float* state, long long slot_stride, long long m_offset,
+                                  int n_heads, float* decay, float* take, float* floor_out, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_heads <= 0) return 0;
+    const int items = n_seqs * n_heads;
+    return (int)launch_pdl(stabilized_gates_kernel, dim3((items + 3) / 4), dim3(128), 0, stream, pre, pre_stride, bias, cap,
+                           cu_q, slots, n_seqs, state, slot_stride, m_offset, n_heads, decay, take, floor_out);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Gates of a state-space recurrence: dt = softplus(dt_pre + dt_bias), decay = exp(-exp(rate_log) * dt), take = dt.
+__global__ void decay_gates_kernel(const float* __restrict__ dt_pre, int stride, const float* __restrict__ dt_bias,
+                                   const float* __restrict__ rate_log, int n_tokens, int n_heads, float* __restrict__ decay,
+                                   float* __restrict__ take) {
+    grid_chain_entry();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * n_heads) return;
+    const int t = i / n_heads, h = i % n_heads;
+    const float z = dt_pre[(size_t)t * stride + h] + dt_bias[h];
+    const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));   // log(1 + e^z), written so that no e^z overflows
+    decay[i] = expf(-expf(rate_log[h]) * dt);
+    take[i] = dt;
+}
+
+QF_EXPORT int qf_decay_gates(const float* dt_pre, int stride, const float* dt_bias, const float* rate_log, int n_tokens,
+                             int n_heads, float* decay, float* take, cudaStream_t stream) {
+    const long long total = (long long)n_tokens * n_heads;
+    if (total <= 0) return 0;
+    return (int)launch_pdl(decay_gates_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, dt_pre, stride,
+                           dt_bias, rate_log, n_tokens, n_heads, decay, take);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// The scan. One warp per (sequence, head, 32 columns of S): lane c keeps its column of S (DPAD floats, the rows beyond
+// `dim` stay zero) in registers from the sequence's first token of the step to its last. The vector n of a matrix memory
+// is one more column whose v is 1 (column index vdim), so a head has ceil((vdim + 1) / 32) warps with it.
+// Tokens are staged SCAN_TOKENS at a time through shared memory (q and k of the head's group, the 32 values, the two
+// gates); a warp is its own block, so staging needs no block barrier.
+#define SCAN_TOKENS 16
+
+template <typename T, int DPAD>
+__global__ void __launch_bounds__(32)
+outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v,
+                        int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
+                        const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
+                        long long slot_stride, long long s_offset, long long n_offset, int n_heads, int n_groups, int dim,
+                        int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq) {
+    grid_chain_entry();
+    __shared__ __align__(16) float q_s[SCAN_TOKENS][DPAD], k_s[SCAN_TOKENS][DPAD];
+    __shared__ float v_s[SCAN_TOKENS][32], decay_s[SCAN_TOKENS], take_s[SCAN_TOKENS];
+    const int lane = threadIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int col = blockIdx.x * 32 + lane;                 // column of S; vdim is the column of n
+    const bool is_n = n_offset >= 0 && col == vdim, active = col < vdim || is_n;
+    const int group = head / (n_heads / n_groups);
+    const int begin = cu_q[seq], end = cu_q[seq + 1], slot = slots[seq];
+    if (begin >= end) return;
+
+    float* column = nullptr;    // the lane's column in the state row: element d at column[d * pitch]
+    int pitch = 0;
+    if (slot >= 0 && active) {
+        float* row = state + slot * slot_stride;
+        column = is_n ? row + n_offset + (long long)head * dim : row + s_offset + (long long)head * dim * vdim + col;
+        pitch = is_n ? 1 : vdim;
+    }
+    float s[DPAD];
+#pragma unroll
+    for (int d = 0; d < DPAD; ++d) s[d] = (column && d < dim) ? column[(size_t)d * pitch] : 0.f;
+
+    for (int t0 = begin; t0 < end; t0 += SCAN_TOKENS) {
+        const int n_here = min(SCAN_TOKENS, end - t0);
+        __syncwarp();
+        for (int i = lane; i < n_here * DPAD; i += 32) {
+            const int j = i / DPAD, d = i % DPAD;
+            const size_t t = t0 + j;
+            q_s[j][d] = d < dim ? Num<T>::to_f(q[t * q_stride + group * dim + d]) * q_scale : 0.f;
+            k_s[j][d] = d < dim ? Num<T>::to_f(k[t * k_stride + group * dim + d]) : 0.f;
+        }
+        for (int j = 0; j < n_here; ++j)
+            v_s[j][lane] = col < vdim ? Num<T>::to_f(v[(size_t)(t0 + j) * v_stride + head * vdim + col]) : 1.f;
+        if (lane < n_here) {
+            decay_s[lane] = decay[(size_t)(t0 + lane) * n_heads + head];
+            take_s[lane] = take[(size_t)(t0 + lane) * n_heads + head];
+        }
+        __syncwarp();
+        for (int j = 0; j < n_here; ++j) {
+            const float keep = decay_s[j], add = take_s[j] * v_s[j][lane];
+            float acc = 0.f;
+#pragma unroll
+            for (int d4 = 0; d4 < DPAD; d4 += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(&k_s[j][d4]);
+                const float4 qq = *reinterpret_cast<const float4*>(&q_s[j][d4]);
+                s[d4] = fmaf(add, kk.x, s[d4] * keep);
+                s[d4 + 1] = fmaf(add, kk.y, s[d4 + 1] * keep);
+                s[d4 + 2] = fmaf(add, kk.z, s[d4 + 2] * keep);
+                s[d4 + 3] = fmaf(add, kk.w, s[d4 + 3] * keep);
+                acc = fmaf(s[d4], qq.x, acc);
+                acc = fmaf(s[d4 + 1], qq.y, acc);
+                acc = fmaf(s[d4 + 2], qq.z, acc);
+                acc = fmaf(s[d4 + 3], qq.w, acc);
+            }
+            const size_t t = t0 + j;
+            if (col < vdim) y[t * ((size_t)n_heads * vdim) + head * vdim + col] = acc;
+            else if (is_n) nq[t * n_heads + head] = acc;
+        }
+    }
+    if (column) {
+#pragma unroll
+        for (int d = 0; d < DPAD; ++d)
+            if (d < dim) column[(size_t)d * pitch] = s[d];
+    }
+}
+
+template <typename T, int DPAD>
+static int launch_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* decay,
+                       const float* take, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
+                       long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
+                       float* y, float* nq, cudaStream_t stream) {
+    const int columns = vdim + (n_offset >= 0 ? 1 : 0);
+    return (int)launch_pdl(outer_state_scan_kernel<T, DPAD>, dim3((columns + 31) / 32, n_heads, n_seqs), dim3(32), 0, stream,
+                           (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay, take, cu_q, slots, state,
+                           slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
+}
+
+#define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
+                     n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, stream
+#define QF_SCAN_CASE(DPAD) \
+    if (dim <= DPAD) return is_bf16 ? launch_scan<bf16, DPAD>(QF_SCAN_ARGS) : launch_scan<float, DPAD>(QF_SCAN_ARGS);
+
+// q, k: [T][groups * dim] with row strides; v: [T][heads * vdim]; decay, take: float32 [T][heads]; y: float32 [T][heads * vdim];
+// nq: float32 [T][heads] or null (then n_offset < 0). State pieces: S [heads][dim][vdim] at s_offset, n [heads][dim] at n_offset.
+QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, const void* k, int k_stride, const void* v,
+                                  int v_stride, const float* decay, const float* take, const int* cu_q, const int* slots,
+                                  int n_seqs, float* state, long long slot_stride, long long s_offset, long long n_offset,
+                                  int n_heads, int n_groups, int dim, int vdim, float q_scale, float* y, float* nq,
+                                  cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
+    QF_SCAN_CASE(16)
+    QF_SCAN_CASE(32)
+    QF_SCAN_CASE(48)
+    QF_SCAN_CASE(64)
+    QF_SCAN_CASE(96)
+    QF_SCAN_CASE(128)
+    QF_SCAN_CASE(192)
+    QF_SCAN_CASE(256)
+    return (int)cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// What follows the scan, one warp per (token, part of the norm). See `ops.gated_group_norm` for the order of the steps.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, const T* __restrict__ weight,
+                        float eps, T* __restrict__ out, int n_tokens, int width, int n_parts, int n_heads, int gate_kind,
+                        int gate_first, const float* __restrict__ nq, const float* __restrict__ floor_in, float floor_add,
+                        const float* __restrict__ skip, const T* __restrict__ skip_x, int skip_stride) {
+    grid_chain_entry();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * n_parts) return;
+    const int t = (int)(item / n_parts), part = (int)(item % n_parts);
+    const int part_width = width / n_parts, head_width = width / n_heads, c0 = part * part_width;
+    auto value = [&](int c, float& g) {
+        const int head = c / head_width;
+        float z = y[(size_t)t * width + c];
+        if (nq) z = z / (fmaxf(fabsf(nq[(size_t)t * n_heads + head]), floor_in[(size_t)t * n_heads + head]) + floor_add);
+        if (skip) z = fmaf(skip[head], Num<T>::to_f(skip_x[(size_t)t * skip_stride + c]), z);
+        const float raw = Num<T>::to_f(gate[(size_t)t * gate_stride + c]);
+        const float sig = 1.f / (1.f + expf(-raw));
+        g = gate_kind == 0 ? sig : raw * sig;
+        return gate_first ? z * g : z;
+    };
+    float sum = 0.f, g;
+    for (int c = c0 + lane; c < c0 + part_width; c += 32) {
+        const float z = value(c, g);
+        sum = fmaf(z, z, sum);
+    }
+    const float inv = rsqrtf(warp_sum(sum) / (float)part_width + eps);
+    for (int c = c0 + lane; c < c0 + part_width; c += 32) {
+        float z = value(c, g) * inv * Num<T>::to_f(weight[c]);
+        if (!gate_first) z *= g;
+        out[(size_t)t * width + c] = Num<T>::from_f(z);
+    }
+}
+
+QF_EXPORT int qf_gated_group_norm(int is_bf16, const float* y, const void* gate, int gate_stride, const void* weight, float eps,
+                                  void* out, int n_tokens, int width, int n_parts, int n_heads, int gate_kind, int gate_first,
+                                  const float* nq, const float* floor_in, float floor_add, const float* skip, const void* skip_x,
+                                  int skip_stride, cudaStream_t stream) {
+    const long long items = (long long)n_tokens * n_parts;
+    if (items <= 0) return 0;
+    if (width % n_parts || width % n_heads) return (int)cudaErrorInvalidValue;
+    const dim3 grid((unsigned)((items + 7) / 8)), block(256);
+    if (is_bf16)
+        return (int)launch_pdl(gated_group_norm_kernel<bf16>, grid, block, 0, stream, y, (const bf16*)gate, gate_stride,
+                               (const bf16*)weight, eps, (bf16*)out, n_tokens, width, n_parts, n_heads, gate_kind, gate_first, nq,
+                               floor_in, floor_add, skip, (const bf16*)skip_x, skip_stride);
+    return (int)launch_pdl(gated_group_norm_kernel<float>, grid, block, 0, stream, y, (const float*)gate, gate_stride,
+                           (const float*)weight, eps, (float*)out, n_tokens, width, n_parts, n_heads, gate_kind, gate_first, nq,
+                           floor_in, floor_add, skip, (const float*)skip_x, skip_stride);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Causal convolution per channel over a sequence's tokens, then silu. A thread takes one (token, channel); what lies
+// before the step's first token comes from the sequence's state (its last taps - 1 inputs). A second kernel then moves
+// the step's last taps - 1 inputs into the state, a thread per (sequence, channel), reading all it needs before it writes.
+#define CONV_MAX_TAPS 16
+
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ weight,
+                                        const float* __restrict__ bias, const int* __restrict__ cu_q,
+                                        const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                                        const float* __restrict__ state, long long slot_stride, long long offset, int taps,
+                                        int n_tokens, int channels, T* __restrict__ out) {
+    grid_chain_entry();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tokens * channels) return;
+    const int t = (int)(i / channels), c = (int)(i % channels);
+    const int seq = tok_seq[t], at = t - cu_q[seq], slot = slots[seq];
+    const float* before = slot >= 0 ? state + slot * slot_stride + offset : nullptr;   // [taps - 1][channels]
+    float z = bias ? bias[c] : 0.f;
+    for (int j = 0; j < taps; ++j) {          // oldest input first: the same order for every cut
+        const int back = taps - 1 - j;
+        float u = 0.f;
+        if (at - back >= 0) u = Num<T>::to_f(x[(size_t)(t - back) * x_stride + c]);
+        else if (before) u = before[(size_t)(taps - 1 + at - back) * channels + c];
+        z = fmaf(weight[(size_t)c * taps + j], u, z);
+    }
+    out[(size_t)t * channels + c] = Num<T>::from_f(z / (1.f + expf(-z)));
+}
+
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ cu_q,
+                                  const int* __restrict__ slots, int n_seqs, float* __restrict__ state, long long slot_stride,
+                                  long long offset, int taps, int channels) {
+    grid_chain_entry();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_seqs * channels) return;
+    const int seq = (int)(i / channels), c = (int)(i % channels);
+    const int slot = slots[seq], begin = cu_q[seq], len = cu_q[seq + 1] - begin;
+    if (slot < 0 || len <= 0) return;
+    float* kept = state + slot * slot_stride + offset;
+    float next[CONV_MAX_TAPS];
+    for (int r = 0; r < taps - 1; ++r) {
+        const int at = len - (taps - 1) + r;   // index among the step's tokens; negative: still one of the old inputs
+        next[r] = at >= 0 ? Num<T>::to_f(x[(size_t)(begin + at) * x_stride + c]) : kept[(size_t)(taps - 1 + at) * channels + c];
+    }
+    for (int r = 0; r < taps - 1; ++r) kept[(size_t)r * channels + c] = next[r];
+}
+
+template <typename T>
+static int launch_conv(const void* x, int x_stride, const float* weight, const float* bias, const int* cu_q, const int* tok_seq,
+                       const int* slots, int n_seqs, float* state, long long slot_stride, long long offset, int taps,
+                       int n_tokens, int channels, void* out, cudaStream_t stream) {
+    const long long total = (long long)n_tokens * channels;
+    cudaError_t e = launch_pdl(causal_conv_silu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                               (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, (const float*)state, slot_stride, offset,
+                               taps, n_tokens, channels, (T*)out);
+    if (e != cudaSuccess || taps <= 1) return (int)e;
+    const long long pairs = (long long)n_seqs * channels;
+    // launched the ordinary way: it must not start before every block of the convolution has read the old state
+    conv_state_kernel<T><<<dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, stream>>>((const T*)x, x_stride, cu_q, slots, n_seqs,
+                                                                                        state, slot_stride, offset, taps, channels);
+    return (int)cudaGetLastError();
+}
+
+QF_EXPORT int qf_causal_conv_silu(int is_bf16, const void* x, int x_stride, const float* weight, const float* bias,
+                                  const int* cu_q, const int* tok_seq, const int* slots, int n_seqs, float* state,
+                                  long long slot_stride, long long offset, int taps, int n_tokens, int channels, void* out,
+                                  cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return 0;
+    if (taps < 1 || taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    return is_bf16 ? launch_conv<bf16>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
+                                       n_tokens, channels, out, stream)
+                   : launch_conv<float>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
+                                        n_tokens, channels, out, stream);
+}

@@ -222,6 +222,87 @@ QF_EXPORT int qf_rope_cache_write(int is_bf16, const void* qkv, const void* bias
                                    stream);
 }
 
+// The same with what other kinds of attention need: after the rotation every q and k head may be divided by its root
+// mean square over its first `norm_dim` components (eps inside the root; eps < 0: no norm), and the rows may hold queries
+// only (`has_kv` 0: a layer that reads another layer's keys and values). One warp per (token, head): the head's
+// components stay in registers between the rotation and the norm. Value heads are copied (with their bias) as they are.
+#define RN_MAX_PER_LANE 16   // head sizes up to 512
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, int qkv_stride, const int* __restrict__ tok_seq,
+                       const int* __restrict__ tok_pos, const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                       int rot_dim, int n_heads, T* __restrict__ q_out, KvSite<T> site, int write_cache, int has_kv,
+                       int norm_dim, float eps, int n_tokens, int* err) {
+    grid_chain_entry();
+    const int D = site.head_dim, KVH = has_kv ? site.kv_heads : 0;
+    const int heads_per_token = n_heads + 2 * KVH;
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * heads_per_token) return;
+    const int t = (int)(item / heads_per_token), head = (int)(item % heads_per_token);
+    const int pos = tok_pos[t], slot = slots[tok_seq[t]];
+    const bool is_q = head < n_heads, is_v = head >= n_heads + KVH;
+    const int src = head * D;      // q heads, then k heads, then v heads, each D wide
+    T* dst = nullptr;
+    if (is_q) {
+        dst = q_out + (size_t)t * n_heads * D + (size_t)head * D;
+    } else if (write_cache && slot >= 0) {
+        dst = kv_row(site, slot, pos, is_v ? head - n_heads - KVH : head - n_heads, is_v ? 1 : 0);
+        if (!dst && lane == 0) atomicOr(err, QF_ERR_NO_PAGE);
+    }
+    if (!dst) return;
+    const T* row = qkv + (size_t)t * qkv_stride + src;
+    const int half = rot_dim / 2;
+    float x[RN_MAX_PER_LANE];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        x[i] = 0.f;
+        if (d >= D) continue;
+        float own = Num<T>::to_f(row[d]) + (bias ? Num<T>::to_f(bias[src + d]) : 0.f);
+        if (!is_v && d < rot_dim) {   // component d turns with its partner d +- rot_dim / 2
+            const int j = d < half ? d : d - half, partner = d < half ? d + half : d - half;
+            const float other = Num<T>::to_f(row[partner]) + (bias ? Num<T>::to_f(bias[src + partner]) : 0.f);
+            float sn, cs;
+            sincosf((float)pos * inv_freq[j], &sn, &cs);
+            own = d < half ? own * cs - other * sn : own * cs + other * sn;
+        }
+        x[i] = own;
+        if (d < norm_dim) sum = fmaf(own, own, sum);
+    }
+    float mult = 1.f;
+    if (!is_v && eps >= 0.f) mult = rsqrtf(warp_sum(sum) / (float)norm_dim + eps);
+#pragma unroll
+    for (int i = 0; i < RN_MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) dst[d] = Num<T>::from_f(x[i] * mult);
+    }
+}
+
+QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void* bias, int qkv_stride, const int* tok_seq,
+                                       const int* tok_pos, const int* slots, const float* inv_freq, int rot_dim, int n_heads,
+                                       void* q_out, void* base, const int* table, long long page_elems, int table_stride,
+                                       int kv_heads, int head_dim, int write_cache, int has_kv, int norm_dim, float eps,
+                                       int n_tokens, int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!inv_freq) rot_dim = 0;
+    if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1) || head_dim > 32 * RN_MAX_PER_LANE || norm_dim <= 0 || norm_dim > head_dim)
+        return (int)cudaErrorInvalidValue;
+    const long long items = (long long)n_tokens * (n_heads + (has_kv ? 2 * kv_heads : 0));
+    const dim3 grid((unsigned)((items + 7) / 8)), block(256);
+    if (is_bf16)
+        return (int)launch_pdl(rope_norm_cache_kernel<bf16>, grid, block, 0, stream, (const bf16*)qkv, (const bf16*)bias, qkv_stride,
+                               tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
+                               KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, has_kv,
+                               norm_dim, eps, n_tokens, err);
+    return (int)launch_pdl(rope_norm_cache_kernel<float>, grid, block, 0, stream, (const float*)qkv, (const float*)bias, qkv_stride,
+                           tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (float*)q_out,
+                           KvSite<float>{(float*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, has_kv,
+                           norm_dim, eps, n_tokens, err);
+}
+
 // The rotation angles of a step, once for all its layers: table[t][j] = (cos, sin) of tok_pos[t] * inv_freq[j], float32,
 // the same expression as in the kernels above.
 __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int n_tokens, int half,
