@@ -44,14 +44,16 @@
 // waiting for anything but its own predecessor.
 __global__ void __launch_bounds__(32)
 decode_plan_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots, int n_seqs,
-                   int kvc, int sms, int warps, int window, int max_splits, int4* __restrict__ plan_all, int n_pairs) {
+                   int kvc, int sms, int warps, int window, int max_splits, int4* __restrict__ plan_all, int n_pairs,
+                   int mask_block) {
     const int lane = threadIdx.x;
     int* runs = reinterpret_cast<int*>(plan_all);
     int4* plan = plan_all + (n_seqs + 3) / 4;
     auto length_of = [&](int s) -> int { return s < n_seqs && slots[s] >= 0 ? tok_pos[cu_q[s]] + 1 : 0; };
     auto pages_of = [&](int len) -> int {
         if (len <= 0) return 0;
-        const int from = window > 0 ? max(0, len - window) : 0;
+        int from = window > 0 ? max(0, len - window) : 0;
+        if (mask_block > 0) from = max(from, (len - 1) / mask_block * mask_block);   // the new token's block of the mask
         return (len - 1) / QF_PAGE - from / QF_PAGE + 1;
     };
     auto runs_of = [&](int pages, float target) -> int {
@@ -105,7 +107,7 @@ template <int D, int WARPS, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                     const int* __restrict__ cu_q, const int4* __restrict__ plan, KvSite<bf16> site, int n_heads, int chunks, float scale_log2,
-                    int window, int max_splits, int n_seqs, int fold_later, float* __restrict__ part_o,
+                    int window, int mask_block, float cap_in, float cap_out, int max_splits, int n_seqs, int fold_later, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int* __restrict__ counters, int* err, unsigned long long* stamps,
                     const float* __restrict__ sinks, int shared_values) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
@@ -161,7 +163,10 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         return;
     }
     const int L = record.z;
-    const int lo = window > 0 ? max(0, L - window) : 0;
+    int lo = window > 0 ? max(0, L - window) : 0;
+    if (mask_block > 0) lo = max(lo, (L - 1) / mask_block * mask_block);   // the new token's block of the mask
+    // capped scores: s <- cap * tanh(s * scale / cap) in base-2 units (cap_in = scale / cap, cap_out = cap * log2(e))
+    const float sl2 = cap_out > 0.f ? 1.f : scale_log2;
     const int first_page = lo / QF_PAGE, last_page = (L - 1) / QF_PAGE;
     const int pps = (last_page - first_page + n_splits) / n_splits;  // ceil(pages / splits)
     const int p_begin = first_page + split * pps, p_end = min(p_begin + pps, last_page + 1);
@@ -295,13 +300,23 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                     mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
                 }
             }
+            if (cap_out > 0.f) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float y;
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(s[t][e] * cap_in));
+                        s[t][e] = cap_out * y;
+                    }
+            }
             const bool full = key0 >= lo && key0 + HALF <= L;  // every key of the half is visible
             float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
             if (full) {
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) s[t][e] *= scale_log2;
+                    for (int e = 0; e < 4; ++e) s[t][e] *= sl2;
                     mx[0] = fmaxf(mx[0], fmaxf(s[t][0], s[t][1]));
                     mx[1] = fmaxf(mx[1], fmaxf(s[t][2], s[t][3]));
                 }
@@ -312,8 +327,8 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                     for (int e = 0; e < 2; ++e) {
                         const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
                         const bool ok = kj >= lo && kj < L;
-                        s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                        s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                        s[t][e] = ok ? s[t][e] * sl2 : QF_NEG_BIG;
+                        s[t][2 + e] = ok ? s[t][2 + e] * sl2 : QF_NEG_BIG;
                         mx[0] = fmaxf(mx[0], s[t][e]);
                         mx[1] = fmaxf(mx[1], s[t][2 + e]);
                     }
@@ -585,7 +600,8 @@ template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int4* plan, void* base, const int* table,
                   long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
                   int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err,
-                  unsigned long long* stamps, const float* sinks, int shared_values, cudaStream_t stream) {
+                  unsigned long long* stamps, const float* sinks, int shared_values, int mask_block, float softcap,
+                  cudaStream_t stream) {
     constexpr int WARPS = decode_warps(D);
     constexpr bool TMA = decode_tma(D);
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
@@ -601,7 +617,8 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
     }
     dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, D, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
-                           (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
+                           (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, mask_block,
+                           softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, n_splits,
                            n_seqs, fold_later, part_o, part_ml, counters, err, stamps, sinks, shared_values);
 }
 
@@ -614,15 +631,21 @@ QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int 
 
 // The plan of one step for attention of this shape (see decode_plan_kernel); the same plan serves every layer of the
 // step that has this shape. `n_splits` is the most runs that one sequence may get.
-QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, int kv_heads,
-                                       int head_dim, int n_heads, int window, int n_splits, void* plan, cudaStream_t stream) {
+QF_EXPORT int qf_attention_decode_plan_masked(const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, int kv_heads,
+                                              int head_dim, int n_heads, int window, int n_splits, void* plan, int mask_block,
+                                              cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || n_splits > 0x7fff || !qf_attention_decode_warps(head_dim))
         return (int)cudaErrorInvalidValue;
     const int kvc = kv_heads * ((n_heads / kv_heads + 15) / 16);
     return (int)launch_pdl(decode_plan_kernel, dim3(1), dim3(32), 0, stream, cu_q, tok_pos, slots, n_seqs, kvc,
                            decode_slots(head_dim), qf_attention_decode_warps(head_dim), window, n_splits, (int4*)plan,
-                           (int)plan_pairs(n_seqs, kv_heads, n_heads, head_dim, n_splits));
+                           (int)plan_pairs(n_seqs, kv_heads, n_heads, head_dim, n_splits), mask_block);
+}
+
+QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, int kv_heads,
+                                       int head_dim, int n_heads, int window, int n_splits, void* plan, cudaStream_t stream) {
+    return qf_attention_decode_plan_masked(cu_q, tok_pos, slots, n_seqs, kv_heads, head_dim, n_heads, window, n_splits, plan, 0, stream);
 }
 
 // Scratch (used when n_splits > 1 or fold_later): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml
@@ -633,14 +656,16 @@ QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, cons
 static int decode_run(const void* q, void* out, const int* cu_q, const void* plan, void* base, const int* table,
                       long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                       float scale, int window, int n_splits, int fold_later, float* part_o, float* part_ml, int* counters,
-                      int* err, unsigned long long* stamps, const float* sinks, int shared_values, cudaStream_t stream) {
+                      int* err, unsigned long long* stamps, const float* sinks, int shared_values, cudaStream_t stream,
+                      int mask_block = 0, float softcap = 0.f) {
     if (n_seqs <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan || (fold_later && sinks)) return (int)cudaErrorInvalidValue;
     if (fold_later ? (!part_o || !part_ml) : !out) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                   \
     case DIM:                                                                                                          \
         return launch<DIM>(q, out, cu_q, (const int4*)plan, base, table, page_elems, table_stride, kv_heads, n_heads, \
-                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, sinks, shared_values, stream);
+                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, sinks, shared_values,   \
+                           mask_block, softcap, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -668,6 +693,19 @@ QF_EXPORT int qf_attention_decode_ex(const void* q, void* out, const int* cu_q, 
                                      int shared_values, cudaStream_t stream) {
     return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
                       window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, sinks, shared_values, stream);
+}
+
+// And with a mask in blocks (`mask_block` > 0: the new token sees only the keys of its own block of that many positions;
+// the plan must have been made with the same value) and capped scores (`softcap` > 0: s <- softcap * tanh(s / softcap)
+// after the scale, with the hardware's approximate tanh).
+QF_EXPORT int qf_attention_decode_masked(const void* q, void* out, const int* cu_q, const void* plan, void* base,
+                                         const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
+                                         int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
+                                         float* part_o, float* part_ml, int* counters, int* err, const float* sinks,
+                                         int shared_values, int mask_block, float softcap, cudaStream_t stream) {
+    return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, sinks, shared_values, stream,
+                      mask_block, softcap);
 }
 
 // A measuring aid: the same launch, with every block's thread 0 writing nanosecond time stamps to stamps[block][8]:

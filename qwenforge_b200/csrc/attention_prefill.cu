@@ -20,13 +20,27 @@
 #define PF_THREADS (PF_WARPS * 32)
 #define PF_BM 64
 
+__device__ __forceinline__ float fast_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                      int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err,
-                     const float* __restrict__ sinks, int shared_values) {
+                     const float* __restrict__ sinks, int shared_values, int mask_block, float cap_in, float cap_out) {
     grid_chain_entry();
+    // capped scores: s <- cap * tanh(s * scale / cap) in base-2 units, cap_in = scale / cap, cap_out = cap * log2(e); the
+    // capped score then needs no further scale
+    const float sl2 = cap_out > 0.f ? 1.f : scale_log2;
+    auto lo_of = [&](int pos) -> int {   // lowest position a query at `pos` sees: its window and its block of the mask
+        int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        if (mask_block > 0) lo = max(lo, pos / mask_block * mask_block);
+        return lo;
+    };
     constexpr int LD = D + 8;
     constexpr int KS = D / 16;
     constexpr int NT = D / 8;
@@ -60,17 +74,17 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     }
     const int pos0 = tok_pos[q_begin + row0];             // position of the tile's first row
     const int last_pos = pos0 + n_rows - 1;
-    const int lo_min = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int lo_min = lo_of(pos0);
     const int p_begin = lo_min / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
 
     // this thread's two rows
     const int r[2] = {16 * warp + (lane >> 2), 16 * warp + (lane >> 2) + 8};
     const bool row_ok[2] = {r[0] < n_rows, r[1] < n_rows};
     const int row_pos[2] = {pos0 + r[0], pos0 + r[1]};
-    const int row_lo[2] = {window > 0 ? max(0, row_pos[0] - window + 1) : 0, window > 0 ? max(0, row_pos[1] - window + 1) : 0};
+    const int row_lo[2] = {lo_of(row_pos[0]), lo_of(row_pos[1])};
     // the warp's rows span positions [warp_first, warp_last]
     const int warp_first = pos0 + 16 * warp, warp_last = min(pos0 + 16 * warp + 15, last_pos);
-    const int warp_lo = window > 0 ? max(0, warp_first - window + 1) : 0;
+    const int warp_lo = lo_of(warp_first);
     const bool warp_active = 16 * warp < n_rows;
 
     uint32_t qa[KS][4];
@@ -137,7 +151,13 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
                 }
             }
             // a page that every row of the warp sees whole needs no mask
-            const bool full = key0 + QF_PAGE - 1 <= warp_first && key0 >= (window > 0 ? max(0, warp_last - window + 1) : 0);
+            if (cap_out > 0.f) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[t][e] = cap_out * fast_tanh(s[t][e] * cap_in);
+            }
+            const bool full = key0 + QF_PAGE - 1 <= warp_first && key0 >= lo_of(warp_last);
             float corr[2], sum[2] = {0.f, 0.f};
             if (full) {
                 // the common case (every page left of the diagonal): no comparisons, one fused multiply-add and one
@@ -153,7 +173,7 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
                 for (int i = 0; i < 2; ++i) {
                     mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                     mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                    const float m_new = fmaxf(m_run[i], mx[i] * scale_log2);
+                    const float m_new = fmaxf(m_run[i], mx[i] * sl2);
                     corr[i] = fast_exp2(m_run[i] - m_new);
                     m_run[i] = m_new;
                     neg_m[i] = -m_new;
@@ -162,8 +182,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
                 for (int t = 0; t < 8; ++t) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        s[t][e] = fast_exp2(fmaf(s[t][e], scale_log2, neg_m[0]));
-                        s[t][2 + e] = fast_exp2(fmaf(s[t][2 + e], scale_log2, neg_m[1]));
+                        s[t][e] = fast_exp2(fmaf(s[t][e], sl2, neg_m[0]));
+                        s[t][2 + e] = fast_exp2(fmaf(s[t][2 + e], sl2, neg_m[1]));
                         sum[0] += s[t][e];
                         sum[1] += s[t][2 + e];
                     }
@@ -177,8 +197,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
                         const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
                         const bool ok0 = kj <= row_pos[0] && kj >= row_lo[0];
                         const bool ok1 = kj <= row_pos[1] && kj >= row_lo[1];
-                        s[t][e] = ok0 ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                        s[t][2 + e] = ok1 ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                        s[t][e] = ok0 ? s[t][e] * sl2 : QF_NEG_BIG;
+                        s[t][2 + e] = ok1 ? s[t][2 + e] * sl2 : QF_NEG_BIG;
                         mx[0] = fmaxf(mx[0], s[t][e]);
                         mx[1] = fmaxf(mx[1], s[t][2 + e]);
                     }
@@ -289,7 +309,7 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
 template <int D, int G>
 static int launch_groups(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, KvSite<bf16> site,
                          int n_heads, int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks,
-                         int shared_values, cudaStream_t stream) {
+                         int shared_values, int mask_block, float softcap, cudaStream_t stream) {
     size_t smem = (size_t)4 * G * QF_PAGE * (D + 8) * sizeof(bf16);
     const size_t merge = (size_t)(G - 1) * PF_WARPS * (D / 8 * 4 + 4) * 32 * sizeof(float);
     if (smem < merge) smem = merge;
@@ -300,14 +320,15 @@ static int launch_groups(const void* q, void* out, const int* cu_q, const int* t
     if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     return (int)launch_pdl(prefill_flash_kernel<D, G>, dim3((unsigned)blocks), dim3(PF_THREADS * G), smem, stream, (const bf16*)q,
                            (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs, n_tiles, qf_sm_count(),
-                           scale * 1.4426950408889634f, window, err, sinks, shared_values);
+                           scale * 1.4426950408889634f, window, err, sinks, shared_values, mask_block,
+                           softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f);
 }
 
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
                   int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, const float* sinks,
-                  int shared_values, cudaStream_t stream) {
+                  int shared_values, int mask_block, float softcap, cudaStream_t stream) {
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     // Two groups of warps per tile when tiles walk many pages and all tiles find room on the SMs at once (a short
     // continuation over a long cache, one prompt of a few thousand tokens): what bounds the kernel then is the longest
@@ -316,27 +337,30 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     // microseconds with one group, 41.6 with two; 16 heads of 128 (512 tiles, room for 296): 73 against 94.
     // (tiles that hold rows: the grid also has blocks for the rows that shorter sequences lack, which end at once)
     const long long tiles = (long long)min((max_q_len + PF_BM - 1) / PF_BM * n_seqs, n_tokens / PF_BM + n_seqs) * n_heads;
-    const int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
+    int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
+    if (mask_block > 0 && mask_block < span) span = mask_block;   // no tile walks more than its rows' block of the mask
     const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * (D <= 64 ? 4 : 2);
-    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream)
-                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, stream);
+    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream)
+                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream);
 }
 
 // The arguments of the generic attention kernel, `n_tokens` (the rows of q: all sequences' new tokens) and `max_kv_len`,
 // an upper bound of any sequence's length after this step (both only steer how a tile's pages are shared among warps);
 // bf16 only. cudaErrorInvalidValue for a head size without an
 // instantiation (the caller then uses the generic kernel).
-QF_EXPORT int qf_attention_prefill_ex(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
-                                      void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
-                                      float scale, int window, int* err, const float* sinks, int shared_values,
-                                      cudaStream_t stream) {
+// mask_block > 0: a query sees only the keys of its own block of that many positions; softcap > 0: a score s (after the
+// scale) becomes softcap * tanh(s / softcap), with the hardware's approximate tanh.
+QF_EXPORT int qf_attention_prefill_masked(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                          void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                          int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                          float scale, int window, int* err, const float* sinks, int shared_values,
+                                          int mask_block, float softcap, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                 \
     case DIM:                                                                                                        \
         return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
-                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, stream);
+                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -346,6 +370,16 @@ QF_EXPORT int qf_attention_prefill_ex(const void* q, void* out, const int* cu_q,
             return (int)cudaErrorInvalidValue;
     }
 #undef QF_CASE
+}
+
+QF_EXPORT int qf_attention_prefill_ex(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                      void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                      float scale, int window, int* err, const float* sinks, int shared_values,
+                                      cudaStream_t stream) {
+    return qf_attention_prefill_masked(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                                       n_heads, n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values,
+                                       0, 0.f, stream);
 }
 
 QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,

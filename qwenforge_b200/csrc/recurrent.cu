@@ -91,29 +91,38 @@ QF_EXPORT int qf_decay_gates(const float* dt_pre, int stride, const float* dt_bi
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// The scan. One warp per (sequence, head, 32 columns of S): lane c keeps its column of S (DPAD floats, the rows beyond
-// `dim` stay zero) in registers from the sequence's first token of the step to its last. The vector n of a matrix memory
-// is one more column whose v is 1 (column index vdim), so a head has ceil((vdim + 1) / 32) warps with it.
-// Tokens are staged SCAN_TOKENS at a time through shared memory (q and k of the head's group, the 32 values, the two
-// gates); a warp is its own block, so staging needs no block barrier.
+// The scan. One block per (sequence, head, 32 columns of S). Lane c of every warp works on column c; the rows of S are
+// dealt out to the block's warps, ROWS to each, and stay in registers from the sequence's first token of the step to its
+// last, so the chain of dependent operations per token is ROWS long instead of dim. Tokens are staged SCAN_TOKENS at a
+// time through shared memory (q and k of the head's group, the 32 values, the two gates); every warp leaves its rows'
+// part of y for the staged tokens in shared memory, and after the tile the parts are added up in the order of the warps.
+// The vector n of a matrix memory is one more column whose v is 1 (column index vdim), so a head has
+// ceil((vdim + 1) / 32) blocks with it. Rows beyond `dim` hold zeros.
 #define SCAN_TOKENS 16
 
-template <typename T, int DPAD>
-__global__ void __launch_bounds__(32)
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(256)
 outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v,
                         int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
                         long long slot_stride, long long s_offset, long long n_offset, int n_heads, int n_groups, int dim,
                         int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq) {
     grid_chain_entry();
-    __shared__ __align__(16) float q_s[SCAN_TOKENS][DPAD], k_s[SCAN_TOKENS][DPAD];
-    __shared__ float v_s[SCAN_TOKENS][32], decay_s[SCAN_TOKENS], take_s[SCAN_TOKENS];
-    const int lane = threadIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    extern __shared__ __align__(16) float scan_smem[];
+    const int warps = blockDim.x >> 5, padded = warps * ROWS;       // padded >= dim
+    float* q_s = scan_smem;                                          // [SCAN_TOKENS][padded]
+    float* k_s = q_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][padded]
+    float* v_s = k_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][32]
+    float* part_s = v_s + SCAN_TOKENS * 32;                          // [warps][SCAN_TOKENS][32]
+    float* decay_s = part_s + warps * SCAN_TOKENS * 32;              // [SCAN_TOKENS]
+    float* take_s = decay_s + SCAN_TOKENS;                           // [SCAN_TOKENS]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, head = blockIdx.y, seq = blockIdx.z;
     const int col = blockIdx.x * 32 + lane;                 // column of S; vdim is the column of n
     const bool is_n = n_offset >= 0 && col == vdim, active = col < vdim || is_n;
     const int group = head / (n_heads / n_groups);
     const int begin = cu_q[seq], end = cu_q[seq + 1], slot = slots[seq];
     if (begin >= end) return;
+    const int d0 = warp * ROWS;                             // this warp's rows of S
 
     float* column = nullptr;    // the lane's column in the state row: element d at column[d * pitch]
     int pitch = 0;
@@ -122,69 +131,85 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         column = is_n ? row + n_offset + (long long)head * dim : row + s_offset + (long long)head * dim * vdim + col;
         pitch = is_n ? 1 : vdim;
     }
-    float s[DPAD];
+    float s[ROWS];
 #pragma unroll
-    for (int d = 0; d < DPAD; ++d) s[d] = (column && d < dim) ? column[(size_t)d * pitch] : 0.f;
+    for (int r = 0; r < ROWS; ++r) s[r] = (column && d0 + r < dim) ? column[(size_t)(d0 + r) * pitch] : 0.f;
 
     for (int t0 = begin; t0 < end; t0 += SCAN_TOKENS) {
         const int n_here = min(SCAN_TOKENS, end - t0);
-        __syncwarp();
-        for (int i = lane; i < n_here * DPAD; i += 32) {
-            const int j = i / DPAD, d = i % DPAD;
+        __syncthreads();   // the tile before is summed and written
+        for (int i = threadIdx.x; i < n_here * padded; i += blockDim.x) {
+            const int j = i / padded, d = i % padded;
             const size_t t = t0 + j;
-            q_s[j][d] = d < dim ? Num<T>::to_f(q[t * q_stride + group * dim + d]) * q_scale : 0.f;
-            k_s[j][d] = d < dim ? Num<T>::to_f(k[t * k_stride + group * dim + d]) : 0.f;
+            q_s[i] = d < dim ? Num<T>::to_f(q[t * q_stride + group * dim + d]) * q_scale : 0.f;
+            k_s[i] = d < dim ? Num<T>::to_f(k[t * k_stride + group * dim + d]) : 0.f;
         }
-        for (int j = 0; j < n_here; ++j)
-            v_s[j][lane] = col < vdim ? Num<T>::to_f(v[(size_t)(t0 + j) * v_stride + head * vdim + col]) : 1.f;
-        if (lane < n_here) {
-            decay_s[lane] = decay[(size_t)(t0 + lane) * n_heads + head];
-            take_s[lane] = take[(size_t)(t0 + lane) * n_heads + head];
+        for (int i = threadIdx.x; i < n_here * 32; i += blockDim.x) {
+            const int j = i >> 5, c = blockIdx.x * 32 + (i & 31);
+            v_s[i] = c < vdim ? Num<T>::to_f(v[(size_t)(t0 + j) * v_stride + head * vdim + c]) : 1.f;
         }
-        __syncwarp();
+        if (threadIdx.x < n_here) {
+            decay_s[threadIdx.x] = decay[(size_t)(t0 + threadIdx.x) * n_heads + head];
+            take_s[threadIdx.x] = take[(size_t)(t0 + threadIdx.x) * n_heads + head];
+        }
+        __syncthreads();
         for (int j = 0; j < n_here; ++j) {
-            const float keep = decay_s[j], add = take_s[j] * v_s[j][lane];
+            const float keep = decay_s[j], add = take_s[j] * v_s[j * 32 + lane];
+            const float* kj = k_s + j * padded + d0;
+            const float* qj = q_s + j * padded + d0;
             float acc = 0.f;
 #pragma unroll
-            for (int d4 = 0; d4 < DPAD; d4 += 4) {
-                const float4 kk = *reinterpret_cast<const float4*>(&k_s[j][d4]);
-                const float4 qq = *reinterpret_cast<const float4*>(&q_s[j][d4]);
-                s[d4] = fmaf(add, kk.x, s[d4] * keep);
-                s[d4 + 1] = fmaf(add, kk.y, s[d4 + 1] * keep);
-                s[d4 + 2] = fmaf(add, kk.z, s[d4 + 2] * keep);
-                s[d4 + 3] = fmaf(add, kk.w, s[d4 + 3] * keep);
-                acc = fmaf(s[d4], qq.x, acc);
-                acc = fmaf(s[d4 + 1], qq.y, acc);
-                acc = fmaf(s[d4 + 2], qq.z, acc);
-                acc = fmaf(s[d4 + 3], qq.w, acc);
+            for (int r4 = 0; r4 < ROWS; r4 += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(kj + r4);
+                const float4 qq = *reinterpret_cast<const float4*>(qj + r4);
+                s[r4] = fmaf(add, kk.x, s[r4] * keep);
+                s[r4 + 1] = fmaf(add, kk.y, s[r4 + 1] * keep);
+                s[r4 + 2] = fmaf(add, kk.z, s[r4 + 2] * keep);
+                s[r4 + 3] = fmaf(add, kk.w, s[r4 + 3] * keep);
+                acc = fmaf(s[r4], qq.x, acc);
+                acc = fmaf(s[r4 + 1], qq.y, acc);
+                acc = fmaf(s[r4 + 2], qq.z, acc);
+                acc = fmaf(s[r4 + 3], qq.w, acc);
             }
+            part_s[(warp * SCAN_TOKENS + j) * 32 + lane] = acc;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_here * 32; i += blockDim.x) {   // the warps' parts in the order of the warps
+            const int j = i >> 5, c = blockIdx.x * 32 + (i & 31);
+            float sum = 0.f;
+            for (int w = 0; w < warps; ++w) sum += part_s[(w * SCAN_TOKENS + j) * 32 + (i & 31)];
             const size_t t = t0 + j;
-            if (col < vdim) y[t * ((size_t)n_heads * vdim) + head * vdim + col] = acc;
-            else if (is_n) nq[t * n_heads + head] = acc;
+            if (c < vdim) y[t * ((size_t)n_heads * vdim) + head * vdim + c] = sum;
+            else if (n_offset >= 0 && c == vdim) nq[t * n_heads + head] = sum;
         }
     }
     if (column) {
 #pragma unroll
-        for (int d = 0; d < DPAD; ++d)
-            if (d < dim) column[(size_t)d * pitch] = s[d];
+        for (int r = 0; r < ROWS; ++r)
+            if (d0 + r < dim) column[(size_t)(d0 + r) * pitch] = s[r];
     }
 }
 
-template <typename T, int DPAD>
+template <typename T, int ROWS>
 static int launch_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* decay,
                        const float* take, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
                        long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
                        float* y, float* nq, cudaStream_t stream) {
     const int columns = vdim + (n_offset >= 0 ? 1 : 0);
-    return (int)launch_pdl(outer_state_scan_kernel<T, DPAD>, dim3((columns + 31) / 32, n_heads, n_seqs), dim3(32), 0, stream,
-                           (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay, take, cu_q, slots, state,
-                           slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
+    const int warps = (dim + ROWS - 1) / ROWS, padded = warps * ROWS;
+    const size_t smem = (size_t)(2 * SCAN_TOKENS * padded + SCAN_TOKENS * 32 + warps * SCAN_TOKENS * 32 + 2 * SCAN_TOKENS) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_pdl(outer_state_scan_kernel<T, ROWS>, dim3((columns + 31) / 32, n_heads, n_seqs), dim3(32 * warps), smem,
+                           stream, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay, take, cu_q, slots,
+                           state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
 }
 
 #define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
                      n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, stream
-#define QF_SCAN_CASE(DPAD) \
-    if (dim <= DPAD) return is_bf16 ? launch_scan<bf16, DPAD>(QF_SCAN_ARGS) : launch_scan<float, DPAD>(QF_SCAN_ARGS);
+// up to eight warps per block: ROWS rows of S per warp cover `dim` rows
+#define QF_SCAN_CASE(ROWS) \
+    if (dim <= 8 * ROWS) return is_bf16 ? launch_scan<bf16, ROWS>(QF_SCAN_ARGS) : launch_scan<float, ROWS>(QF_SCAN_ARGS);
 
 // q, k: [T][groups * dim] with row strides; v: [T][heads * vdim]; decay, take: float32 [T][heads]; y: float32 [T][heads * vdim];
 // nq: float32 [T][heads] or null (then n_offset < 0). State pieces: S [heads][dim][vdim] at s_offset, n [heads][dim] at n_offset.
@@ -195,14 +220,10 @@ QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, cons
                                   cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
+    QF_SCAN_CASE(4)
+    QF_SCAN_CASE(8)
     QF_SCAN_CASE(16)
     QF_SCAN_CASE(32)
-    QF_SCAN_CASE(48)
-    QF_SCAN_CASE(64)
-    QF_SCAN_CASE(96)
-    QF_SCAN_CASE(128)
-    QF_SCAN_CASE(192)
-    QF_SCAN_CASE(256)
     return (int)cudaErrorInvalidValue;
 }
 

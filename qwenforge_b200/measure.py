@@ -9,6 +9,7 @@ attention kernels compare. Every figure is the mean of CUDA-graph replays timed 
     python -m qwenforge_b200.measure attention --tokens 1024,2048,4096 --heads 14 --kv-heads 2 --head-dim 64
     python -m qwenforge_b200.measure decode-attention --lengths 4000,4000,4000,4000,4000,4000,4000,4000 --splits 8
     python -m qwenforge_b200.measure gemm --preset qwen2.5-0.5b --rows 2048,16384
+    python -m qwenforge_b200.measure scan --tokens 2048,8192 --heads 28 --head-dim 128 --vdim 64 --batch 8
 
 products   per product of a layer (output projection, gate/up, down, query/key/value): the weight-streaming kernel of
            skinny_gemm.cu (rows <= 16), the tcgen05 kernel of wide_gemm.cu (rows <= 64; after the norm kernel where the
@@ -20,6 +21,7 @@ attention  the mma.sync and the tcgen05 prefill attention on one prompt, with a 
 decode-attention  the split-K decode attention's own time stamps (launched alone, cold caches): which runs the plan
            gives every sequence, and when a block's copies, pages, merge, ticket and fold end; with and without the
            projection that folds the partial results
+scan       the recurrence of the recurrent mixers (recurrent.cu) alone, on a prompt and on a decode step
 gemm       a feed-forward's gate/up product on many rows: the library product, the library product and the gate kernel,
            this library's tcgen05 product (one tile per block, and persistent) plain and with the gate in its epilogue
 """
@@ -413,9 +415,44 @@ def measure_gemm(args) -> None:
             raise RuntimeError(f"a kernel reported error word {int(err)}")
 
 
+def measure_scan(args) -> None:
+    """The recurrent scan alone: a prompt of --tokens tokens and a decode step of --batch sequences, --heads heads whose
+    state is --head-dim x --vdim, with the bytes that have to move (inputs, outputs, the state once in and once out) and
+    the float32 operations (3 per element of S and token: decay, update, read) beside the time."""
+    heads, dim, vdim, groups = args.heads, args.head_dim, args.vdim, args.groups
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for tokens, seqs in [(t, 1) for t in args.tokens] + [(args.batch, args.batch)]:
+        per = tokens // seqs
+        wide = torch.randn(tokens, 2 * groups * dim + heads * vdim, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        q, k, v = wide[:, :groups * dim], wide[:, groups * dim:2 * groups * dim], wide[:, 2 * groups * dim:]
+        decay = torch.rand(tokens, heads, generator=g, device="cuda")
+        take = torch.rand(tokens, heads, generator=g, device="cuda")
+        cu_q = torch.arange(0, tokens + 1, per, dtype=torch.int32, device="cuda")
+        slots = torch.arange(seqs, dtype=torch.int32, device="cuda")
+        state = torch.zeros(seqs, heads * dim * vdim, device="cuda")
+        y = torch.empty(tokens, heads * vdim, device="cuda")
+        run = lambda: ops.outer_state_scan(q, k, v, decay, take, cu_q, slots, state, 0, -1, heads, groups, dim, vdim, 1.0, y, None)
+        for _ in range(3):
+            run()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for _ in range(10):
+            start.record()
+            run()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end) * 1e3)
+        us = sorted(times)[len(times) // 2]
+        moved = wide.numel() * 2 + y.numel() * 4 + 2 * state.numel() * 4 + 2 * decay.numel() * 4
+        flops = 6.0 * tokens * heads * dim * vdim
+        what = f"prompt of {tokens} tokens" if seqs == 1 else f"decode step of {seqs} sequences"
+        print(f"scan, {heads} heads of {dim} x {vdim}, {what}: {us:8.1f} us, {moved / 1e6:7.2f} MB ({moved / us / 1e3:6.1f} GB/s), "
+              f"{flops / us / 1e6:6.2f} TFLOP/s float32", flush=True)
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="qwenforge_b200.measure", description=__doc__.split("\n\n")[0])
-    p.add_argument("what", choices=["products", "chain", "phases", "attention", "decode-attention", "gemm"])
+    p.add_argument("what", choices=["products", "chain", "phases", "attention", "decode-attention", "gemm", "scan"])
     p.add_argument("--preset", default="qwen2.5-0.5b")
     p.add_argument("--rows", default="8", type=lambda text: [int(v) for v in text.split(",")])
     p.add_argument("--repeat", type=int, default=12, help="layers, each with weights of its own, captured into one graph")
@@ -426,11 +463,14 @@ def main(argv=None) -> int:
     p.add_argument("--lengths", default="4000,4000,4000,4000,4000,4000,4000,4000", type=lambda text: [int(v) for v in text.split(",")],
                    help="decode-attention: the sequences' lengths")
     p.add_argument("--splits", type=int, default=8, help="decode-attention: the most runs of pages per sequence")
+    p.add_argument("--vdim", type=int, default=64, help="scan: columns of a head's state")
+    p.add_argument("--groups", type=int, default=1, help="scan: groups of heads that share q and k")
+    p.add_argument("--batch", type=int, default=8, help="scan: sequences of the decode step")
     args = p.parse_args(argv)
     ops.require_cuda("cuda", "the measurement")
     with torch.inference_mode():
         {"products": measure_products, "chain": measure_chain, "phases": measure_phases, "attention": measure_attention,
-         "decode-attention": measure_decode_attention, "gemm": measure_gemm}[args.what](args)
+         "decode-attention": measure_decode_attention, "gemm": measure_gemm, "scan": measure_scan}[args.what](args)
     return 0
 
 

@@ -298,9 +298,10 @@ FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
                       window: int, err: torch.Tensor, max_kv_len: Optional[int] = None,
-                      sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
+                      sinks: Optional[torch.Tensor] = None, shared_values: bool = False, chunk: int = 0,
+                      softcap: float = 0.0) -> None:
     """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128.
-    `sinks`, `shared_values`: as in `attention_generic`.
+    `sinks`, `shared_values`, `chunk`, `softcap`: as in `attention_generic` (the cap with the hardware's approximate tanh).
     `max_kv_len`: an upper bound of any sequence's length after the step (None: unknown, taken as long); it only
     steers whether a tile of rows shares its pages among two groups of warps."""
     _dev("q", q, torch.bfloat16)
@@ -316,11 +317,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         _dev("sinks", sinks, torch.float32)
         if sinks.numel() != n_heads:
             raise KernelError("attention_prefill: sinks must hold one float32 per query head")
-    _check(library("attention_prefill").qf_attention_prefill_ex(
+    _check(library("attention_prefill").qf_attention_prefill_masked(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
         _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err),
-        _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_prefill")
+        _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _stream()), "attention_prefill")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)
@@ -388,7 +389,8 @@ def attention_decode_warps(head_dim: int) -> int:
 
 
 def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, kv_heads: int, head_dim: int,
-                          n_heads: int, n_seqs: int, window: int, n_splits: int, scratch: DecodeScratch) -> torch.Tensor:
+                          n_heads: int, n_seqs: int, window: int, n_splits: int, scratch: DecodeScratch,
+                          chunk: int = 0) -> torch.Tensor:
     """The plan of one decode step for attention of this shape: which block takes which run of which sequence, worked
     out on the device from the batch's lengths (sequences of unequal lengths get blocks of about equal work; a batch
     that fills the SMs unsplit stays unsplit). One plan serves every layer of the step with this shape. `n_splits` is
@@ -405,22 +407,25 @@ def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torc
     records = int(lib.qf_attention_decode_plan_size(_I(n_seqs), _I(kv_heads), _I(n_heads), _I(head_dim), _I(n_splits)))
     if records <= 0:
         raise KernelError(f"attention_decode: head_dim {head_dim} has no tensor-core kernel (have {FAST_ATTENTION_HEAD_DIMS})")
-    plan = scratch.plan((n_seqs, kv_heads, n_heads, head_dim, window, n_splits), records)
-    _check(lib.qf_attention_decode_plan(_ptr(cu_q), _ptr(tok_pos), _ptr(slots), _I(n_seqs), _I(kv_heads), _I(head_dim),
-                                        _I(n_heads), _I(window), _I(n_splits), _ptr(plan), _stream()), "attention_decode_plan")
+    plan = scratch.plan((n_seqs, kv_heads, n_heads, head_dim, window, n_splits, chunk), records)
+    _check(lib.qf_attention_decode_plan_masked(_ptr(cu_q), _ptr(tok_pos), _ptr(slots), _I(n_seqs), _I(kv_heads), _I(head_dim),
+                                               _I(n_heads), _I(window), _I(n_splits), _ptr(plan), _I(int(chunk)), _stream()),
+           "attention_decode_plan")
     return plan
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, scale: float, window: int,
                      n_splits: int, scratch: DecodeScratch, err: torch.Tensor, plan: Optional[torch.Tensor] = None,
-                     fold_later: bool = False, sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
+                     fold_later: bool = False, sinks: Optional[torch.Tensor] = None, shared_values: bool = False,
+                     chunk: int = 0, softcap: float = 0.0) -> None:
     """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128.
     `n_splits` is the most blocks that share one (sequence, kv head); `plan` (attention_decode_plan with the same
     shape, made in this step; made here when absent) says how many of them each sequence gets. With `fold_later` the
     kernel stops at the runs' partial results in `scratch` and writes no `out` (which may be None): `fold_project`
-    folds them on its way into the output projection. `sinks`, `shared_values`: as in `attention_generic` (sinks not
-    with `fold_later`)."""
+    folds them on its way into the output projection. `sinks`, `shared_values`, `chunk`, `softcap`: as in
+    `attention_generic` (sinks not with `fold_later`; a given `plan` must have been made with the same `chunk`; the cap
+    with the hardware's approximate tanh)."""
     _dev("q", q, torch.bfloat16)
     if sinks is not None:
         _dev("sinks", sinks, torch.float32)
@@ -438,18 +443,18 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok
     if not 1 <= n_splits <= 128:
         raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..128")
     if plan is None:
-        plan = attention_decode_plan(cu_q, tok_pos, slots, site.kv_heads, d, n_heads, n_seqs, window, n_splits, scratch)
+        plan = attention_decode_plan(cu_q, tok_pos, slots, site.kv_heads, d, n_heads, n_seqs, window, n_splits, scratch, chunk)
     group = n_heads // site.kv_heads
     n_counters = n_seqs * site.kv_heads * ((group + 15) // 16)
     partials = n_splits > 1 or fold_later
     if partials:
         scratch.ensure(n_seqs, n_heads, n_splits, d, n_counters)
-    _check(library("attention_decode").qf_attention_decode_ex(
+    _check(library("attention_decode").qf_attention_decode_masked(
         _ptr(q), _ptr(None if fold_later else out), _ptr(cu_q), _ptr(plan), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _F(scale),
         _I(window), _I(n_splits), _I(1 if fold_later else 0), _ptr(scratch.part_o if partials else None),
         _ptr(scratch.part_ml if partials else None), _ptr(scratch.counters if partials else None), _ptr(err),
-        _ptr(sinks), _I(int(bool(shared_values))), _stream()), "attention_decode")
+        _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _stream()), "attention_decode")
 
 
 class _FoldProjectArgs(ctypes.Structure):

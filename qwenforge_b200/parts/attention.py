@@ -81,11 +81,11 @@ class GqaAttention(Mixer):
 
     def tensor_specs(self):
         kd, vd = self.key_dim, self.value_dim
-        specs = [TensorSpec(self.file_name("q_weight"), (self.n_heads * kd, self.hidden)),
-                 TensorSpec(self.file_name("o_weight"), (self.hidden, self.n_heads * vd))]
+        specs = [TensorSpec(self.file_name("q_weight"), (self.n_heads * kd, self.hidden))]
         if self.own_kv:
             specs += [TensorSpec(self.file_name("k_weight"), (self.n_kv * kd, self.hidden)),
                       TensorSpec(self.file_name("v_weight"), (self.n_kv * vd, self.hidden))]
+        specs.append(TensorSpec(self.file_name("o_weight"), (self.hidden, self.n_heads * vd)))
         if self.qkv_bias:
             specs.append(TensorSpec(self.file_name("q_bias"), (self.n_heads * kd,), init="bias"))
             if self.own_kv:
@@ -99,7 +99,9 @@ class GqaAttention(Mixer):
         libs = {"rope_cache", "attention_generic"}
         if dtype == torch.float32:
             libs.add("gemm_f32")
-        elif self.plain and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
+        elif not self.plain and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
+            libs |= {"attention_decode", "attention_prefill", "skinny_gemm"}
+        elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
             libs |= {"attention_decode", "attention_prefill", "skinny_gemm", "wide_gemm", "fold_project"}
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 libs.add("attention_prefill_tc")
@@ -196,9 +198,20 @@ class GqaAttention(Mixer):
                              ctx.err, bias=self.qkv_bias_t, unit_norm_eps=self.unit_norm_eps, norm_dim=self.key_dim,
                              has_kv=self.own_kv)
         attended = torch.empty_like(q)
-        ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
-                              self.scale, self.window, ctx.err, scratch=ctx.decode_scratch, max_kv_len=ctx.max_kv_len,
-                              sinks=self.sinks, chunk=self.chunk, softcap=self.softcap)
+        fast = ctx.attention == "auto" and x.dtype == torch.bfloat16 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS
+        if fast and ctx.is_decode and n == ctx.n_seqs:
+            n_splits = self.decode_splits(ctx)
+            ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, self.scale,
+                                 self.window, n_splits, ctx.decode_scratch, ctx.err, self.decode_plan(ctx), sinks=self.sinks,
+                                 chunk=self.chunk, softcap=self.softcap)
+        elif fast:
+            ops.attention_prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
+                                  self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len, sinks=self.sinks,
+                                  chunk=self.chunk, softcap=self.softcap)
+        else:
+            ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
+                                  self.scale, self.window, ctx.err, scratch=ctx.decode_scratch, max_kv_len=ctx.max_kv_len,
+                                  sinks=self.sinks, chunk=self.chunk, softcap=self.softcap)
         return ops.linear(attended, self.o_weight, self.o_bias_t) if self.o_bias_t is not None else ops.linear_rows(attended, self.o_weight)
 
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,
@@ -264,12 +277,13 @@ class GqaAttention(Mixer):
         """Which block of the decode attention takes which run of which sequence: made once per step, by the first
         layer of this shape that runs, and shared through the step's memo by the others."""
         n_splits = self.decode_splits(ctx)
-        key = ("gqa_attention.decode_plan", self.n_kv, self.n_heads, self.head_dim, self.window, n_splits)
+        key = ("gqa_attention.decode_plan", self.n_kv, self.n_heads, self.head_dim, self.window, n_splits, self.chunk)
         memo = ctx.step_memo if ctx.step_memo is not None else {}
         plan = memo.get(key)
         if plan is None:
             plan = memo[key] = ops.attention_decode_plan(ctx.cu_q, ctx.tok_pos, ctx.slots, self.n_kv, self.head_dim,
-                                                         self.n_heads, ctx.n_seqs, self.window, n_splits, ctx.decode_scratch)
+                                                         self.n_heads, ctx.n_seqs, self.window, n_splits, ctx.decode_scratch,
+                                                         self.chunk)
         return plan
 
     def decode_splits(self, ctx) -> int:
@@ -278,6 +292,8 @@ class GqaAttention(Mixer):
         How many of them a sequence gets is the kernel's decision, from the lengths on the device; this number sizes
         its grid and scratch and depends on the batch's shape only (fixed inside a captured graph)."""
         span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + PAGE_TOKENS)
+        if self.chunk > 0:
+            span = min(span, self.chunk + PAGE_TOKENS)
         pages = max(1, -(-span // PAGE_TOKENS))
         warps = ops.attention_decode_warps(self.head_dim)
         return max(1, min(-(-pages // warps), 64))

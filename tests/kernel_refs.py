@@ -316,7 +316,7 @@ def stabilized_gates(pre, bias, cap, cu_q, slots, state, m_offset, n_heads, deca
     f = torch.nn.functional.logsigmoid(cap * torch.tanh(z[:, n_heads:] / cap))
     for s in range(cu_q.numel() - 1):
         slot = int(slots[s])
-        m = _f(state[slot, m_offset:m_offset + n_heads]) if slot >= 0 else torch.zeros(n_heads, dtype=torch.float64)
+        m = _f(state[slot, m_offset:m_offset + n_heads]) if slot >= 0 else torch.zeros(n_heads, dtype=torch.float64, device=pre.device)
         for t in range(int(cu_q[s]), int(cu_q[s + 1])):
             m_new = torch.maximum(f[t] + m, a[t])
             decay[t] = torch.exp(f[t] + m - m_new).float()
@@ -337,8 +337,8 @@ def outer_state_scan(q, k, v, decay, take, cu_q, slots, state, s_offset, n_offse
     per = n_heads // n_groups
     for s in range(cu_q.numel() - 1):
         slot = int(slots[s])
-        S = torch.zeros(n_heads, dim, vdim, dtype=torch.float64)
-        nv = torch.zeros(n_heads, dim, dtype=torch.float64)
+        S = torch.zeros(n_heads, dim, vdim, dtype=torch.float64, device=q.device)
+        nv = torch.zeros(n_heads, dim, dtype=torch.float64, device=q.device)
         if slot >= 0:
             S = _f(state[slot, s_offset:s_offset + n_heads * dim * vdim]).view(n_heads, dim, vdim).clone()
             if nq is not None:
@@ -385,7 +385,7 @@ def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
     for s in range(cu_q.numel() - 1):
         b, e = int(cu_q[s]), int(cu_q[s + 1])
         slot = int(slots[s])
-        before = torch.zeros(taps - 1, c, dtype=torch.float64)
+        before = torch.zeros(taps - 1, c, dtype=torch.float64, device=x.device)
         if slot >= 0:
             before = _f(state[slot, offset:offset + (taps - 1) * c]).view(taps - 1, c)
         padded = torch.cat((before, _f(x[b:e])))

@@ -117,3 +117,13 @@ def test_portions_down_to_two_tokens(reference_kernels, tmp_path):
         at += size
     assert at == len(tokens)
     assert max_err(torch.cat(got), plain.forward_logits(ZEB_ONES, weights, tokens)) < 5e-5
+
+
+def test_presets_are_valid_configurations():
+    from qwenforge_b200.config import preset_config, preset_names
+    from qwenforge_b200.engine import Model
+    names = [n for n in preset_names() if n.startswith("zebovik")]
+    assert {"zebovik-tiny", "zebovik-0.5b", "zebovik-3b"} <= set(names)
+    for name in names:
+        spec = preset_config(name).model_spec()
+        assert len(Model.tensor_specs_of(spec)) > 0 and any(e.cache_from is not None for e in spec.schedule)

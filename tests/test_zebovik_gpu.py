@@ -37,9 +37,12 @@ def logits_close(got, want, dtype, what=""):
     err = d.square().mean(-1).sqrt() / want.std(-1)
     if dtype == torch.float32:
         assert float(err.max()) <= 1e-4, f"{what}: worst row {float(err.max()):.3e} exceeds 1e-4"
-    else:
-        assert float(err.max()) <= 0.25 and float(err.median()) <= 0.06, \
-            f"{what}: worst row {float(err.max()):.3e}, median {float(err.median()):.3e}"
+    else:   # the typical row within rounding, and no row lost: a wrong key, a mask one position off or a lost state moves
+        # every later row by about its whole spread, which the median sees; a single row whose sharp softmax magnifies
+        # the rounding of its scores may stand out
+        far = float((err > 0.4).double().mean())
+        assert float(err.median()) <= 0.05 and far <= 0.02 and float(err.max()) <= 1.0, \
+            f"{what}: median {float(err.median()):.3e}, {far:.1%} of the rows over 0.4, worst {float(err.max()):.3e}"
 
 
 def rand(g, *shape, dtype=torch.float32, spread=1.0):
@@ -157,6 +160,42 @@ def test_attention_in_blocks_with_capped_scores_and_a_unit_sink(dtype, heads, kv
         close(out, want, dtype, f"spans {span}", f32=2e-5, bf16=2e-2)
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,chunk,cap", [(4, 1, 64, 128, 30.0), (8, 4, 96, 200, 30.0), (2, 2, 32, 70, 0.0), (6, 2, 128, 64, 4.0)])
+def test_tensor_core_attention_takes_the_block_mask_the_cap_and_the_sink(heads, kv_heads, dim, chunk, cap):
+    """The bfloat16 kernels of prompts and of single tokens with the same options, against the reference: prompts,
+    continuations across a block's edge, single tokens just inside and just outside a block, long and short together."""
+    from qwenforge_b200 import ops
+    from qwenforge_b200.cache import KvNeed, SequenceCache
+    g = torch.Generator().manual_seed(chunk)
+    dtype = torch.bfloat16
+    cache = SequenceCache([KvNeed(kv_heads, dim)], 4096, 4, 2048, dtype, DEV)
+    slots = [cache.open() for _ in range(3)]
+    cache.reserve([(slots[0], 1500), (slots[1], 420), (slots[2], 420)])
+    cache.flush()
+    site = cache.site(0)
+    site.storage.copy_(rand(g, *site.storage.shape, dtype=dtype))
+    args = ops.KvSiteArgs(site.storage, site.table, kv_heads, dim)
+    sinks = torch.zeros(heads, dtype=torch.float32, device=DEV)
+    scratch = ops.DecodeScratch(DEV)
+    spans = [[(0, 1100), (0, 300), (0, 90)], [(chunk * 2 - 3, 9), (290, 70), (0, 2)],
+             [(1499, 1), (299, 1), (chunk, 1)], [(2 * chunk - 1, 1), (2 * chunk, 1), (89, 1)], [(5 * chunk + 1, 1), (419, 1), (chunk - 1, 1)]]
+    for span in spans:
+        batch = Batch(slots, span)
+        q = rand(g, batch.n_tokens, heads * dim, dtype=dtype, spread=1.5)
+        out, want = torch.empty_like(q), torch.empty_like(q)
+        err = torch.zeros(1, dtype=torch.int32, device=DEV)
+        if batch.max_q_len == 1:
+            ops.attention_decode(q, out, batch.cu_q, batch.tok_pos, batch.slots, args, heads, 3, 0.3, 0, 4, scratch, err,
+                                 sinks=sinks, chunk=chunk, softcap=cap)
+        else:
+            ops.attention_prefill(q, out, batch.cu_q, batch.tok_pos, batch.slots, args, heads, 3, batch.max_q_len, 0.3, 0, err,
+                                  max_kv_len=batch.max_kv_len, sinks=sinks, chunk=chunk, softcap=cap)
+        refs.attention_generic(q, want, batch.cu_q, batch.tok_pos, batch.slots, site, heads, 3, batch.max_q_len, 0.3, 0, err,
+                               sinks=sinks, chunk=chunk, softcap=cap)
+        assert int(err) == 0
+        close(out, want, dtype, f"spans {span}", bf16=2e-2)
+
+
 def test_stabilized_gates_carry_their_maximum():
     from qwenforge_b200 import ops
     g = torch.Generator().manual_seed(3)
@@ -258,7 +297,12 @@ def test_causal_conv_keeps_its_last_inputs(dtype, taps, channels):
 
 # ------------------------------------------------------------------------------------------------ the model
 def build(cfg, folder, dtype, seed=0, weights=None):
+    """The model on the GPU and the weights it holds: in bfloat16 the plain implementation gets the rounded weights, so
+    that the comparison sees the arithmetic and not the rounding of the file."""
     from qwenforge_b200.engine import Model
+    weights = plain.random_weights(cfg, seed) if weights is None else weights
+    if dtype == torch.bfloat16:
+        weights = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
     folder, weights = make_model_dir(cfg, seed, folder, weights=weights)
     return Model.from_dir(folder, dtype, DEV), weights, folder
 
