@@ -12,58 +12,71 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------------------------------
-// Exponential gates with a running maximum (the mLSTM's): one warp per (sequence, head). The lanes take 32 tokens at a
-// time: each works out its token's two log gates (tanh, logsigmoid), then the maximum runs through the 32 in order,
-// then each lane forms its token's three exponentials.
+// Exponential gates with a running maximum (the mLSTM's): one block per (sequence, head), GATE_TOKENS tokens at a time.
+// Every thread works out its token's two log gates (tanh, logsigmoid); then the first warp runs the maximum through the
+// tokens in order, 32 at a time, each lane handing its pair to the chain by shuffle; then every thread forms its token's
+// three exponentials. The chain's additions are the same, in the same order, for every cut of the sequence.
+#define GATE_TOKENS 256
+
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(GATE_TOKENS)
 stabilized_gates_kernel(const float* __restrict__ pre, int pre_stride, const float* __restrict__ bias, float cap,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, int n_seqs, float* __restrict__ state,
                         long long slot_stride, long long m_offset, int n_heads, float* __restrict__ decay,
                         float* __restrict__ take, float* __restrict__ floor_out) {
     grid_chain_entry();
-    const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= n_seqs * n_heads) return;
-    const int seq = item / n_heads, head = item % n_heads;
+    __shared__ float a_s[GATE_TOKENS], f_s[GATE_TOKENS], before_s[GATE_TOKENS], after_s[GATE_TOKENS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int seq = blockIdx.x / n_heads, head = blockIdx.x % n_heads;
     const int begin = cu_q[seq], end = cu_q[seq + 1], slot = slots[seq];
     float* m_ptr = slot >= 0 ? state + slot * slot_stride + m_offset + head : nullptr;
-    float m = m_ptr ? *m_ptr : 0.f;
+    float m = m_ptr ? *m_ptr : 0.f;          // the first warp's copy is the one that runs
     const float bi = bias[head], bf = bias[n_heads + head];
-    for (int t0 = begin; t0 < end; t0 += 32) {
-        const int t = t0 + lane;
+    for (int t0 = begin; t0 < end; t0 += GATE_TOKENS) {
+        const int t = t0 + threadIdx.x, n_here = min(GATE_TOKENS, end - t0);
         float a = 0.f, f = 0.f;
         if (t < end) {
             a = cap * tanhf((pre[(size_t)t * pre_stride + head] + bi) / cap);
             f = log_sigmoid(cap * tanhf((pre[(size_t)t * pre_stride + n_heads + head] + bf) / cap));
         }
-        float m_before = 0.f, m_mine = 0.f;
-        const int n_here = min(32, end - t0);
-        for (int j = 0; j < n_here; ++j) {   // the same additions in the same order for every cut of the sequence
-            const float aj = __shfl_sync(0xffffffffu, a, j), fj = __shfl_sync(0xffffffffu, f, j);
-            const float m_new = fmaxf(fj + m, aj);
-            if (lane == j) {
-                m_before = m;
-                m_mine = m_new;
+        a_s[threadIdx.x] = a;
+        f_s[threadIdx.x] = f;
+        __syncthreads();
+        if (warp == 0) {
+            for (int r0 = 0; r0 < n_here; r0 += 32) {
+                const float ar = a_s[r0 + lane], fr = f_s[r0 + lane];
+                float m_before = 0.f, m_mine = 0.f;
+                const int count = min(32, n_here - r0);
+                for (int j = 0; j < count; ++j) {
+                    const float aj = __shfl_sync(0xffffffffu, ar, j), fj = __shfl_sync(0xffffffffu, fr, j);
+                    const float m_new = fmaxf(fj + m, aj);
+                    if (lane == j) {
+                        m_before = m;
+                        m_mine = m_new;
+                    }
+                    m = m_new;
+                }
+                before_s[r0 + lane] = m_before;
+                after_s[r0 + lane] = m_mine;
             }
-            m = m_new;
         }
+        __syncthreads();
         if (t < end) {
+            const float m_before = before_s[threadIdx.x], m_mine = after_s[threadIdx.x];
             decay[(size_t)t * n_heads + head] = expf(f + m_before - m_mine);
             take[(size_t)t * n_heads + head] = expf(a - m_mine);
             floor_out[(size_t)t * n_heads + head] = expf(-m_mine);
         }
     }
-    if (m_ptr && lane == 0) *m_ptr = m;
+    if (m_ptr && threadIdx.x == 0) *m_ptr = m;
 }
 
 QF_EXPORT int qf_stabilized_gates(const float* pre, int pre_stride, const float* bias, float cap, const int* cu_q,
                                   const int* slots, int n_seqs, float* state, long long slot_stride, long long m_offset,
                                   int n_heads, float* decay, float* take, float* floor_out, cudaStream_t stream) {
     if (n_seqs <= 0 || n_heads <= 0) return 0;
-    const int items = n_seqs * n_heads;
-    return (int)launch_pdl(stabilized_gates_kernel, dim3((items + 3) / 4), dim3(128), 0, stream, pre, pre_stride, bias, cap,
+    return (int)launch_pdl(stabilized_gates_kernel, dim3(n_seqs * n_heads), dim3(GATE_TOKENS), 0, stream, pre, pre_stride, bias, cap,
                            cu_q, slots, n_seqs, state, slot_stride, m_offset, n_heads, decay, take, floor_out);
 }
 
@@ -92,16 +105,32 @@ QF_EXPORT int qf_decay_gates(const float* dt_pre, int stride, const float* dt_bi
 
 // ------------------------------------------------------------------------------------------------------------------
 // The scan. One block per (sequence, head, 32 columns of S). Lane c of every warp works on column c; the rows of S are
-// dealt out to the block's warps, ROWS to each, and stay in registers from the sequence's first token of the step to its
+// dealt out to the block's sixteen warps, ROWS to each, and stay in registers from the sequence's first token of the step to its
 // last, so the chain of dependent operations per token is ROWS long instead of dim. Tokens are staged SCAN_TOKENS at a
 // time through shared memory (q and k of the head's group, the 32 values, the two gates); every warp leaves its rows'
 // part of y for the staged tokens in shared memory, and after the tile the parts are added up in the order of the warps.
+// The next tile's inputs are fetched into registers before a tile is worked on, so their way from memory is hidden.
 // The vector n of a matrix memory is one more column whose v is 1 (column index vdim), so a head has
 // ceil((vdim + 1) / 32) blocks with it. Rows beyond `dim` hold zeros.
+// A load that stays where it is written: the next tile's inputs are asked for BEFORE the work on this tile, and a
+// compiler that moved the loads down to their first use would put their way from memory back on the critical path.
+__device__ __forceinline__ float load_early(const float* p) {
+    float x;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(x) : "l"(p));
+    return x;
+}
+__device__ __forceinline__ float load_early(const bf16* p) {
+    unsigned short raw;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(p));
+    return __uint_as_float((unsigned)raw << 16);
+}
+
 #define SCAN_TOKENS 16
+#define SCAN_WARPS 16
+#define SCAN_THREADS (SCAN_WARPS * 32)
 
 template <typename T, int ROWS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(SCAN_THREADS)
 outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v,
                         int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
@@ -109,7 +138,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                         int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq) {
     grid_chain_entry();
     extern __shared__ __align__(16) float scan_smem[];
-    const int warps = blockDim.x >> 5, padded = warps * ROWS;       // padded >= dim
+    constexpr int warps = SCAN_WARPS, padded = SCAN_WARPS * ROWS;    // padded >= dim
     float* q_s = scan_smem;                                          // [SCAN_TOKENS][padded]
     float* k_s = q_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][padded]
     float* v_s = k_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][32]
@@ -135,43 +164,86 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) s[r] = (column && d0 + r < dim) ? column[(size_t)(d0 + r) * pitch] : 0.f;
 
+    // A tile's inputs are fetched into registers while the tile before is worked on, and put into shared memory when that
+    // one is done: a thread holds ROWS / 2 elements of q and of k (SCAN_TOKENS * padded / SCAN_THREADS), two of v, a gate.
+    constexpr int QK_EACH = ROWS / 2;
+    constexpr int V_EACH = SCAN_TOKENS * 32 / SCAN_THREADS;
+    float q_next[QK_EACH], k_next[QK_EACH], v_next[V_EACH], gate_next[2] = {0.f, 0.f};
+    auto fetch = [&](int t0) {
+        const int n_here = min(SCAN_TOKENS, end - t0);
+#pragma unroll
+        for (int u = 0; u < QK_EACH; ++u) {
+            const int i = threadIdx.x + u * SCAN_THREADS, j = i / padded, d = i % padded;
+            const bool there = j < n_here && d < dim;
+            const size_t t = t0 + j;
+            q_next[u] = there ? load_early(q + t * q_stride + group * dim + d) * q_scale : 0.f;
+            k_next[u] = there ? load_early(k + t * k_stride + group * dim + d) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < V_EACH; ++u) {
+            const int i = threadIdx.x + u * SCAN_THREADS, j = i >> 5, c = blockIdx.x * 32 + (i & 31);
+            v_next[u] = 0.f;
+            if (i < SCAN_TOKENS * 32 && j < n_here) v_next[u] = c < vdim ? load_early(v + (size_t)(t0 + j) * v_stride + head * vdim + c) : 1.f;
+        }
+        if (threadIdx.x < n_here) {
+            gate_next[0] = load_early(decay + (size_t)(t0 + threadIdx.x) * n_heads + head);
+            gate_next[1] = load_early(take + (size_t)(t0 + threadIdx.x) * n_heads + head);
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int u = 0; u < QK_EACH; ++u) {
+            q_s[threadIdx.x + u * SCAN_THREADS] = q_next[u];
+            k_s[threadIdx.x + u * SCAN_THREADS] = k_next[u];
+        }
+#pragma unroll
+        for (int u = 0; u < V_EACH; ++u) {
+            const int i = threadIdx.x + u * SCAN_THREADS;
+            if (i < SCAN_TOKENS * 32) v_s[i] = v_next[u];
+        }
+        if (threadIdx.x < SCAN_TOKENS) {
+            decay_s[threadIdx.x] = gate_next[0];
+            take_s[threadIdx.x] = gate_next[1];
+        }
+    };
+
+    fetch(begin);
     for (int t0 = begin; t0 < end; t0 += SCAN_TOKENS) {
         const int n_here = min(SCAN_TOKENS, end - t0);
         __syncthreads();   // the tile before is summed and written
-        for (int i = threadIdx.x; i < n_here * padded; i += blockDim.x) {
-            const int j = i / padded, d = i % padded;
-            const size_t t = t0 + j;
-            q_s[i] = d < dim ? Num<T>::to_f(q[t * q_stride + group * dim + d]) * q_scale : 0.f;
-            k_s[i] = d < dim ? Num<T>::to_f(k[t * k_stride + group * dim + d]) : 0.f;
-        }
-        for (int i = threadIdx.x; i < n_here * 32; i += blockDim.x) {
-            const int j = i >> 5, c = blockIdx.x * 32 + (i & 31);
-            v_s[i] = c < vdim ? Num<T>::to_f(v[(size_t)(t0 + j) * v_stride + head * vdim + c]) : 1.f;
-        }
-        if (threadIdx.x < n_here) {
-            decay_s[threadIdx.x] = decay[(size_t)(t0 + threadIdx.x) * n_heads + head];
-            take_s[threadIdx.x] = take[(size_t)(t0 + threadIdx.x) * n_heads + head];
-        }
+        stash();
         __syncthreads();
-        for (int j = 0; j < n_here; ++j) {
+        if (t0 + SCAN_TOKENS < end) fetch(t0 + SCAN_TOKENS);   // on its way while this tile is worked on
+        auto token = [&](int j) {
             const float keep = decay_s[j], add = take_s[j] * v_s[j * 32 + lane];
             const float* kj = k_s + j * padded + d0;
             const float* qj = q_s + j * padded + d0;
-            float acc = 0.f;
+            float4 kk[ROWS / 4], qq[ROWS / 4];   // all of the token's rows asked for at once: one wait, not one per four rows
 #pragma unroll
-            for (int r4 = 0; r4 < ROWS; r4 += 4) {
-                const float4 kk = *reinterpret_cast<const float4*>(kj + r4);
-                const float4 qq = *reinterpret_cast<const float4*>(qj + r4);
-                s[r4] = fmaf(add, kk.x, s[r4] * keep);
-                s[r4 + 1] = fmaf(add, kk.y, s[r4 + 1] * keep);
-                s[r4 + 2] = fmaf(add, kk.z, s[r4 + 2] * keep);
-                s[r4 + 3] = fmaf(add, kk.w, s[r4 + 3] * keep);
-                acc = fmaf(s[r4], qq.x, acc);
-                acc = fmaf(s[r4 + 1], qq.y, acc);
-                acc = fmaf(s[r4 + 2], qq.z, acc);
-                acc = fmaf(s[r4 + 3], qq.w, acc);
+            for (int r = 0; r < ROWS / 4; ++r) {
+                kk[r] = *reinterpret_cast<const float4*>(kj + 4 * r);
+                qq[r] = *reinterpret_cast<const float4*>(qj + 4 * r);
             }
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS / 4; ++r) {
+                s[4 * r] = fmaf(add, kk[r].x, s[4 * r] * keep);
+                s[4 * r + 1] = fmaf(add, kk[r].y, s[4 * r + 1] * keep);
+                s[4 * r + 2] = fmaf(add, kk[r].z, s[4 * r + 2] * keep);
+                s[4 * r + 3] = fmaf(add, kk[r].w, s[4 * r + 3] * keep);
+                a0 = fmaf(s[4 * r], qq[r].x, a0);
+                a1 = fmaf(s[4 * r + 1], qq[r].y, a1);
+                a2 = fmaf(s[4 * r + 2], qq[r].z, a2);
+                a3 = fmaf(s[4 * r + 3], qq[r].w, a3);
+            }
+            const float acc = (a0 + a1) + (a2 + a3);
             part_s[(warp * SCAN_TOKENS + j) * 32 + lane] = acc;
+        };
+        if (n_here == SCAN_TOKENS) {   // a whole tile: the tokens' code laid out one after another, addresses as constants
+#pragma unroll
+            for (int j = 0; j < SCAN_TOKENS; ++j) token(j);
+        } else {
+            for (int j = 0; j < n_here; ++j) token(j);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < n_here * 32; i += blockDim.x) {   // the warps' parts in the order of the warps
@@ -196,7 +268,7 @@ static int launch_scan(const void* q, int q_stride, const void* k, int k_stride,
                        long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
                        float* y, float* nq, cudaStream_t stream) {
     const int columns = vdim + (n_offset >= 0 ? 1 : 0);
-    const int warps = (dim + ROWS - 1) / ROWS, padded = warps * ROWS;
+    constexpr int warps = SCAN_WARPS, padded = SCAN_WARPS * ROWS;
     const size_t smem = (size_t)(2 * SCAN_TOKENS * padded + SCAN_TOKENS * 32 + warps * SCAN_TOKENS * 32 + 2 * SCAN_TOKENS) * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -207,9 +279,9 @@ static int launch_scan(const void* q, int q_stride, const void* k, int k_stride,
 
 #define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
                      n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, stream
-// up to eight warps per block: ROWS rows of S per warp cover `dim` rows
+// sixteen warps per block: ROWS rows of S per warp cover `dim` rows
 #define QF_SCAN_CASE(ROWS) \
-    if (dim <= 8 * ROWS) return is_bf16 ? launch_scan<bf16, ROWS>(QF_SCAN_ARGS) : launch_scan<float, ROWS>(QF_SCAN_ARGS);
+    if (dim <= SCAN_WARPS * ROWS) return is_bf16 ? launch_scan<bf16, ROWS>(QF_SCAN_ARGS) : launch_scan<float, ROWS>(QF_SCAN_ARGS);
 
 // q, k: [T][groups * dim] with row strides; v: [T][heads * vdim]; decay, take: float32 [T][heads]; y: float32 [T][heads * vdim];
 // nq: float32 [T][heads] or null (then n_offset < 0). State pieces: S [heads][dim][vdim] at s_offset, n [heads][dim] at n_offset.
@@ -222,8 +294,8 @@ QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, cons
     if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
     QF_SCAN_CASE(4)
     QF_SCAN_CASE(8)
+    QF_SCAN_CASE(12)
     QF_SCAN_CASE(16)
-    QF_SCAN_CASE(32)
     return (int)cudaErrorInvalidValue;
 }
 
