@@ -48,7 +48,7 @@ stabilized_gates_kernel(const float* __restrict__ pre, int pre_stride, const flo
                 const float ar = a_s[r0 + lane], fr = f_s[r0 + lane];
                 float m_before = 0.f, m_mine = 0.f;
                 const int count = min(32, n_here - r0);
-                for (int j = 0; j < count; ++j) {
+                auto link = [&](int j) {
                     const float aj = __shfl_sync(0xffffffffu, ar, j), fj = __shfl_sync(0xffffffffu, fr, j);
                     const float m_new = fmaxf(fj + m, aj);
                     if (lane == j) {
@@ -56,6 +56,12 @@ stabilized_gates_kernel(const float* __restrict__ pre, int pre_stride, const flo
                         m_mine = m_new;
                     }
                     m = m_new;
+                };
+                if (count == 32) {   // laid out link after link: the shuffles go ahead, an addition and a maximum per token remain
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) link(j);
+                } else {
+                    for (int j = 0; j < count; ++j) link(j);
                 }
                 before_s[r0 + lane] = m_before;
                 after_s[r0 + lane] = m_mine;
@@ -104,14 +110,15 @@ QF_EXPORT int qf_decay_gates(const float* dt_pre, int stride, const float* dt_bi
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// The scan. One block per (sequence, head, 32 columns of S). Lane c of every warp works on column c; the rows of S are
-// dealt out to the block's sixteen warps, ROWS to each, and stay in registers from the sequence's first token of the step to its
-// last, so the chain of dependent operations per token is ROWS long instead of dim. Tokens are staged SCAN_TOKENS at a
-// time through shared memory (q and k of the head's group, the 32 values, the two gates); every warp leaves its rows'
-// part of y for the staged tokens in shared memory, and after the tile the parts are added up in the order of the warps.
-// The next tile's inputs are fetched into registers before a tile is worked on, so their way from memory is hidden.
+// The scan. One block per (sequence, head, 16 columns of S). A half warp works on the 16 columns; the rows of S are dealt
+// out to the block's half warps, ROWS to each, and stay in registers from the sequence's first token of the step to its
+// last, so the chain of dependent operations per token is ROWS long instead of dim, and a head's state is spread over
+// vdim / 16 SMs. Tokens are staged SCAN_TOKENS at a time through shared memory (q and k of the head's group, the 16
+// values, the two gates); every half warp leaves its rows' part of y for the staged tokens in shared memory, and after
+// the tile the parts are added up in the order of the half warps. The next tile's inputs are fetched into registers
+// before a tile is worked on, so their way from memory is hidden.
 // The vector n of a matrix memory is one more column whose v is 1 (column index vdim), so a head has
-// ceil((vdim + 1) / 32) blocks with it. Rows beyond `dim` hold zeros.
+// ceil((vdim + 1) / 16) blocks with it. Rows beyond `dim` hold zeros.
 // A load that stays where it is written: the next tile's inputs are asked for BEFORE the work on this tile, and a
 // compiler that moved the loads down to their first use would put their way from memory back on the critical path.
 __device__ __forceinline__ float load_early(const float* p) {
@@ -125,12 +132,11 @@ __device__ __forceinline__ float load_early(const bf16* p) {
     return __uint_as_float((unsigned)raw << 16);
 }
 
-#define SCAN_TOKENS 16
-#define SCAN_WARPS 16
-#define SCAN_THREADS (SCAN_WARPS * 32)
+#define SCAN_TOKENS 32
+#define SCAN_COLS 16
 
-template <typename T, int ROWS>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <typename T, int WARPS, int ROWS>
+__global__ void __launch_bounds__(32 * WARPS)
 outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v,
                         int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
@@ -138,20 +144,21 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                         int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq) {
     grid_chain_entry();
     extern __shared__ __align__(16) float scan_smem[];
-    constexpr int warps = SCAN_WARPS, padded = SCAN_WARPS * ROWS;    // padded >= dim
+    constexpr int THREADS = 32 * WARPS, PARTS = 2 * WARPS, padded = PARTS * ROWS;   // padded >= dim
     float* q_s = scan_smem;                                          // [SCAN_TOKENS][padded]
     float* k_s = q_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][padded]
-    float* v_s = k_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][32]
-    float* part_s = v_s + SCAN_TOKENS * 32;                          // [warps][SCAN_TOKENS][32]
-    float* decay_s = part_s + warps * SCAN_TOKENS * 32;              // [SCAN_TOKENS]
+    float* v_s = k_s + SCAN_TOKENS * padded;                         // [SCAN_TOKENS][SCAN_COLS]
+    float* part_s = v_s + SCAN_TOKENS * SCAN_COLS;                   // [PARTS][SCAN_TOKENS][SCAN_COLS]
+    float* decay_s = part_s + PARTS * SCAN_TOKENS * SCAN_COLS;       // [SCAN_TOKENS]
     float* take_s = decay_s + SCAN_TOKENS;                           // [SCAN_TOKENS]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, head = blockIdx.y, seq = blockIdx.z;
-    const int col = blockIdx.x * 32 + lane;                 // column of S; vdim is the column of n
+    const int c16 = lane & 15, part = warp * 2 + (lane >> 4);
+    const int col = blockIdx.x * SCAN_COLS + c16;           // column of S; vdim is the column of n
     const bool is_n = n_offset >= 0 && col == vdim, active = col < vdim || is_n;
     const int group = head / (n_heads / n_groups);
     const int begin = cu_q[seq], end = cu_q[seq + 1], slot = slots[seq];
     if (begin >= end) return;
-    const int d0 = warp * ROWS;                             // this warp's rows of S
+    const int d0 = part * ROWS;                             // this half warp's rows of S
 
     float* column = nullptr;    // the lane's column in the state row: element d at column[d * pitch]
     int pitch = 0;
@@ -165,15 +172,15 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     for (int r = 0; r < ROWS; ++r) s[r] = (column && d0 + r < dim) ? column[(size_t)(d0 + r) * pitch] : 0.f;
 
     // A tile's inputs are fetched into registers while the tile before is worked on, and put into shared memory when that
-    // one is done: a thread holds ROWS / 2 elements of q and of k (SCAN_TOKENS * padded / SCAN_THREADS), two of v, a gate.
-    constexpr int QK_EACH = ROWS / 2;
-    constexpr int V_EACH = SCAN_TOKENS * 32 / SCAN_THREADS;
+    // one is done: a thread holds ROWS elements of q and of k (SCAN_TOKENS * padded / THREADS), one or two of v, a gate.
+    constexpr int QK_EACH = SCAN_TOKENS * padded / THREADS;
+    constexpr int V_EACH = (SCAN_TOKENS * SCAN_COLS + THREADS - 1) / THREADS;
     float q_next[QK_EACH], k_next[QK_EACH], v_next[V_EACH], gate_next[2] = {0.f, 0.f};
     auto fetch = [&](int t0) {
         const int n_here = min(SCAN_TOKENS, end - t0);
 #pragma unroll
         for (int u = 0; u < QK_EACH; ++u) {
-            const int i = threadIdx.x + u * SCAN_THREADS, j = i / padded, d = i % padded;
+            const int i = threadIdx.x + u * THREADS, j = i / padded, d = i % padded;
             const bool there = j < n_here && d < dim;
             const size_t t = t0 + j;
             q_next[u] = there ? load_early(q + t * q_stride + group * dim + d) * q_scale : 0.f;
@@ -181,9 +188,10 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         }
 #pragma unroll
         for (int u = 0; u < V_EACH; ++u) {
-            const int i = threadIdx.x + u * SCAN_THREADS, j = i >> 5, c = blockIdx.x * 32 + (i & 31);
+            const int i = threadIdx.x + u * THREADS, j = i / SCAN_COLS, c = blockIdx.x * SCAN_COLS + i % SCAN_COLS;
             v_next[u] = 0.f;
-            if (i < SCAN_TOKENS * 32 && j < n_here) v_next[u] = c < vdim ? load_early(v + (size_t)(t0 + j) * v_stride + head * vdim + c) : 1.f;
+            if (i < SCAN_TOKENS * SCAN_COLS && j < n_here)
+                v_next[u] = c < vdim ? load_early(v + (size_t)(t0 + j) * v_stride + head * vdim + c) : 1.f;
         }
         if (threadIdx.x < n_here) {
             gate_next[0] = load_early(decay + (size_t)(t0 + threadIdx.x) * n_heads + head);
@@ -193,13 +201,13 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     auto stash = [&]() {
 #pragma unroll
         for (int u = 0; u < QK_EACH; ++u) {
-            q_s[threadIdx.x + u * SCAN_THREADS] = q_next[u];
-            k_s[threadIdx.x + u * SCAN_THREADS] = k_next[u];
+            q_s[threadIdx.x + u * THREADS] = q_next[u];
+            k_s[threadIdx.x + u * THREADS] = k_next[u];
         }
 #pragma unroll
         for (int u = 0; u < V_EACH; ++u) {
-            const int i = threadIdx.x + u * SCAN_THREADS;
-            if (i < SCAN_TOKENS * 32) v_s[i] = v_next[u];
+            const int i = threadIdx.x + u * THREADS;
+            if (i < SCAN_TOKENS * SCAN_COLS) v_s[i] = v_next[u];
         }
         if (threadIdx.x < SCAN_TOKENS) {
             decay_s[threadIdx.x] = gate_next[0];
@@ -215,7 +223,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         __syncthreads();
         if (t0 + SCAN_TOKENS < end) fetch(t0 + SCAN_TOKENS);   // on its way while this tile is worked on
         auto token = [&](int j) {
-            const float keep = decay_s[j], add = take_s[j] * v_s[j * 32 + lane];
+            const float keep = decay_s[j], add = take_s[j] * v_s[j * SCAN_COLS + c16];
             const float* kj = k_s + j * padded + d0;
             const float* qj = q_s + j * padded + d0;
             float4 kk[ROWS / 4], qq[ROWS / 4];   // all of the token's rows asked for at once: one wait, not one per four rows
@@ -236,8 +244,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                 a2 = fmaf(s[4 * r + 2], qq[r].z, a2);
                 a3 = fmaf(s[4 * r + 3], qq[r].w, a3);
             }
-            const float acc = (a0 + a1) + (a2 + a3);
-            part_s[(warp * SCAN_TOKENS + j) * 32 + lane] = acc;
+            part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = (a0 + a1) + (a2 + a3);
         };
         if (n_here == SCAN_TOKENS) {   // a whole tile: the tokens' code laid out one after another, addresses as constants
 #pragma unroll
@@ -246,10 +253,11 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
             for (int j = 0; j < n_here; ++j) token(j);
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < n_here * 32; i += blockDim.x) {   // the warps' parts in the order of the warps
-            const int j = i >> 5, c = blockIdx.x * 32 + (i & 31);
+        for (int i = threadIdx.x; i < n_here * SCAN_COLS; i += THREADS) {   // the parts in the order of the half warps
+            const int j = i / SCAN_COLS, c = blockIdx.x * SCAN_COLS + i % SCAN_COLS;
             float sum = 0.f;
-            for (int w = 0; w < warps; ++w) sum += part_s[(w * SCAN_TOKENS + j) * 32 + (i & 31)];
+#pragma unroll 4
+            for (int w = 0; w < PARTS; ++w) sum += part_s[(w * SCAN_TOKENS + j) * SCAN_COLS + i % SCAN_COLS];
             const size_t t = t0 + j;
             if (c < vdim) y[t * ((size_t)n_heads * vdim) + head * vdim + c] = sum;
             else if (n_offset >= 0 && c == vdim) nq[t * n_heads + head] = sum;
@@ -262,26 +270,27 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     }
 }
 
-template <typename T, int ROWS>
+template <typename T, int WARPS, int ROWS>
 static int launch_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* decay,
                        const float* take, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
                        long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
                        float* y, float* nq, cudaStream_t stream) {
     const int columns = vdim + (n_offset >= 0 ? 1 : 0);
-    constexpr int warps = SCAN_WARPS, padded = SCAN_WARPS * ROWS;
-    const size_t smem = (size_t)(2 * SCAN_TOKENS * padded + SCAN_TOKENS * 32 + warps * SCAN_TOKENS * 32 + 2 * SCAN_TOKENS) * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    constexpr int PARTS = 2 * WARPS, padded = PARTS * ROWS;
+    const size_t smem = (size_t)(2 * SCAN_TOKENS * padded + SCAN_TOKENS * SCAN_COLS + PARTS * SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, WARPS, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_pdl(outer_state_scan_kernel<T, ROWS>, dim3((columns + 31) / 32, n_heads, n_seqs), dim3(32 * warps), smem,
-                           stream, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay, take, cu_q, slots,
-                           state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
+    return (int)launch_pdl(outer_state_scan_kernel<T, WARPS, ROWS>, dim3((columns + SCAN_COLS - 1) / SCAN_COLS, n_heads, n_seqs),
+                           dim3(32 * WARPS), smem, stream, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay,
+                           take, cu_q, slots, state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
 }
 
 #define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
                      n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, stream
-// sixteen warps per block: ROWS rows of S per warp cover `dim` rows
-#define QF_SCAN_CASE(ROWS) \
-    if (dim <= SCAN_WARPS * ROWS) return is_bf16 ? launch_scan<bf16, ROWS>(QF_SCAN_ARGS) : launch_scan<float, ROWS>(QF_SCAN_ARGS);
+// 2 * WARPS half warps of ROWS rows each cover `dim` rows
+#define QF_SCAN_CASE(WARPS, ROWS) \
+    if (dim <= 2 * WARPS * ROWS)  \
+        return is_bf16 ? launch_scan<bf16, WARPS, ROWS>(QF_SCAN_ARGS) : launch_scan<float, WARPS, ROWS>(QF_SCAN_ARGS);
 
 // q, k: [T][groups * dim] with row strides; v: [T][heads * vdim]; decay, take: float32 [T][heads]; y: float32 [T][heads * vdim];
 // nq: float32 [T][heads] or null (then n_offset < 0). State pieces: S [heads][dim][vdim] at s_offset, n [heads][dim] at n_offset.
@@ -292,65 +301,106 @@ QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, cons
                                   cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
-    QF_SCAN_CASE(4)
-    QF_SCAN_CASE(8)
-    QF_SCAN_CASE(12)
-    QF_SCAN_CASE(16)
+    QF_SCAN_CASE(4, 4)
+    QF_SCAN_CASE(8, 4)
+    QF_SCAN_CASE(16, 4)
+    QF_SCAN_CASE(16, 8)
     return (int)cudaErrorInvalidValue;
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// What follows the scan, one warp per (token, part of the norm). See `ops.gated_group_norm` for the order of the steps.
-template <typename T>
+// What follows the scan, one pass per token and part of the norm. See `ops.gated_group_norm` for the order of the steps.
+#define NORM_KEEP 8   // values of a part that a thread keeps in registers
+
+// G threads per (token, part): a warp for parts of up to 256 elements, a block of 256 threads beyond. A part of up to
+// NORM_KEEP * G elements stays in registers and every input is read once, all loads of a thread asked for together;
+// longer parts are computed twice.
+template <typename T, int G>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, const T* __restrict__ weight,
                         float eps, T* __restrict__ out, int n_tokens, int width, int n_parts, int n_heads, int gate_kind,
                         int gate_first, const float* __restrict__ nq, const float* __restrict__ floor_in, float floor_add,
                         const float* __restrict__ skip, const T* __restrict__ skip_x, int skip_stride) {
     grid_chain_entry();
-    const int lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (long long)n_tokens * n_parts) return;
-    const int t = (int)(item / n_parts), part = (int)(item % n_parts);
-    const int part_width = width / n_parts, head_width = width / n_heads, c0 = part * part_width;
-    auto value = [&](int c, float& g) {
+    __shared__ float scratch[33];
+    const int member = threadIdx.x % G;
+    const long long item = (long long)blockIdx.x * (256 / G) + threadIdx.x / G;
+    const bool live = item < (long long)n_tokens * n_parts;   // (a warp is live or not as a whole; a block of G = 256 too)
+    const int t = live ? (int)(item / n_parts) : 0, part = live ? (int)(item % n_parts) : 0;
+    const int part_width = width / n_parts, head_width = width / n_heads, c0 = part * part_width, c_end = c0 + part_width;
+    auto gate_of = [&](int c) {
+        const float raw = Num<T>::to_f(gate[(size_t)t * gate_stride + c]);
+        const float sig = 1.f / (1.f + expf(-raw));
+        return gate_kind == 0 ? sig : raw * sig;
+    };
+    auto value = [&](int c) {
         const int head = c / head_width;
         float z = y[(size_t)t * width + c];
         if (nq) z = z / (fmaxf(fabsf(nq[(size_t)t * n_heads + head]), floor_in[(size_t)t * n_heads + head]) + floor_add);
         if (skip) z = fmaf(skip[head], Num<T>::to_f(skip_x[(size_t)t * skip_stride + c]), z);
-        const float raw = Num<T>::to_f(gate[(size_t)t * gate_stride + c]);
-        const float sig = 1.f / (1.f + expf(-raw));
-        g = gate_kind == 0 ? sig : raw * sig;
-        return gate_first ? z * g : z;
+        return gate_first ? z * gate_of(c) : z;
     };
-    float sum = 0.f, g;
-    for (int c = c0 + lane; c < c0 + part_width; c += 32) {
-        const float z = value(c, g);
-        sum = fmaf(z, z, sum);
+    auto total = [&](float v) {
+        if (G == 32) return warp_sum(v);
+        return block_sum(v, scratch);
+    };
+    if (G == 32 && !live) return;
+    const bool single = part_width <= NORM_KEEP * G;
+    float kept[NORM_KEEP], sum = 0.f;
+    if (single) {
+#pragma unroll
+        for (int i = 0; i < NORM_KEEP; ++i) {
+            const int c = c0 + member + G * i;
+            kept[i] = live && c < c_end ? value(c) : 0.f;
+            sum = fmaf(kept[i], kept[i], sum);
+        }
+    } else if (live) {
+        for (int c = c0 + member; c < c_end; c += G) {
+            const float z = value(c);
+            sum = fmaf(z, z, sum);
+        }
     }
-    const float inv = rsqrtf(warp_sum(sum) / (float)part_width + eps);
-    for (int c = c0 + lane; c < c0 + part_width; c += 32) {
-        float z = value(c, g) * inv * Num<T>::to_f(weight[c]);
-        if (!gate_first) z *= g;
-        out[(size_t)t * width + c] = Num<T>::from_f(z);
+    const float inv = rsqrtf(total(sum) / (float)part_width + eps);
+    if (!live) return;
+    if (single) {
+#pragma unroll
+        for (int i = 0; i < NORM_KEEP; ++i) {
+            const int c = c0 + member + G * i;
+            if (c >= c_end) continue;
+            float z = kept[i] * inv * Num<T>::to_f(weight[c]);
+            if (!gate_first) z *= gate_of(c);
+            out[(size_t)t * width + c] = Num<T>::from_f(z);
+        }
+    } else {
+        for (int c = c0 + member; c < c_end; c += G) {
+            float z = value(c) * inv * Num<T>::to_f(weight[c]);
+            if (!gate_first) z *= gate_of(c);
+            out[(size_t)t * width + c] = Num<T>::from_f(z);
+        }
     }
+}
+
+template <typename T, int G>
+static int launch_norm(const float* y, const void* gate, int gate_stride, const void* weight, float eps, void* out, int n_tokens,
+                       int width, int n_parts, int n_heads, int gate_kind, int gate_first, const float* nq, const float* floor_in,
+                       float floor_add, const float* skip, const void* skip_x, int skip_stride, cudaStream_t stream) {
+    const long long items = (long long)n_tokens * n_parts, per_block = 256 / G;
+    return (int)launch_pdl(gated_group_norm_kernel<T, G>, dim3((unsigned)((items + per_block - 1) / per_block)), dim3(256), 0, stream,
+                           y, (const T*)gate, gate_stride, (const T*)weight, eps, (T*)out, n_tokens, width, n_parts, n_heads,
+                           gate_kind, gate_first, nq, floor_in, floor_add, skip, (const T*)skip_x, skip_stride);
 }
 
 QF_EXPORT int qf_gated_group_norm(int is_bf16, const float* y, const void* gate, int gate_stride, const void* weight, float eps,
                                   void* out, int n_tokens, int width, int n_parts, int n_heads, int gate_kind, int gate_first,
                                   const float* nq, const float* floor_in, float floor_add, const float* skip, const void* skip_x,
                                   int skip_stride, cudaStream_t stream) {
-    const long long items = (long long)n_tokens * n_parts;
-    if (items <= 0) return 0;
+    if ((long long)n_tokens * n_parts <= 0) return 0;
     if (width % n_parts || width % n_heads) return (int)cudaErrorInvalidValue;
-    const dim3 grid((unsigned)((items + 7) / 8)), block(256);
-    if (is_bf16)
-        return (int)launch_pdl(gated_group_norm_kernel<bf16>, grid, block, 0, stream, y, (const bf16*)gate, gate_stride,
-                               (const bf16*)weight, eps, (bf16*)out, n_tokens, width, n_parts, n_heads, gate_kind, gate_first, nq,
-                               floor_in, floor_add, skip, (const bf16*)skip_x, skip_stride);
-    return (int)launch_pdl(gated_group_norm_kernel<float>, grid, block, 0, stream, y, (const float*)gate, gate_stride,
-                           (const float*)weight, eps, (float*)out, n_tokens, width, n_parts, n_heads, gate_kind, gate_first, nq,
-                           floor_in, floor_add, skip, (const float*)skip_x, skip_stride);
+#define QF_NORM_ARGS y, gate, gate_stride, weight, eps, out, n_tokens, width, n_parts, n_heads, gate_kind, gate_first, nq, floor_in, \
+                     floor_add, skip, skip_x, skip_stride, stream
+    if (width / n_parts <= 32 * NORM_KEEP) return is_bf16 ? launch_norm<bf16, 32>(QF_NORM_ARGS) : launch_norm<float, 32>(QF_NORM_ARGS);
+    return is_bf16 ? launch_norm<bf16, 256>(QF_NORM_ARGS) : launch_norm<float, 256>(QF_NORM_ARGS);
+#undef QF_NORM_ARGS
 }
 
 // ------------------------------------------------------------------------------------------------------------------
