@@ -19,7 +19,7 @@ def attention(heads, kv_heads, dim, vdim, mask, rot_dims, base=10000.0, scale=No
     return "attention", m
 
 
-def mlstm(heads, dim, vdim, gate_cap=15.0):
+def mlstm(heads, dim, vdim, gate_cap=10.0):
     return "mlstm", dict(heads=heads, dim=dim, vdim=vdim, gate_cap=gate_cap)
 
 

@@ -129,7 +129,7 @@ def test_rotation_unit_norm_and_cache_write(dtype, heads, kv_heads, dim, norm_di
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("heads,kv_heads,dim,chunk,cap", [(4, 2, 14, 37, 5.0), (4, 1, 64, 128, 30.0), (3, 3, 24, 1, 0.0), (2, 2, 96, 200, 2.0)])
+@pytest.mark.parametrize("heads,kv_heads,dim,chunk,cap", [(4, 2, 14, 37, 5.0), (4, 1, 64, 128, 20.0), (3, 3, 24, 1, 0.0), (2, 2, 96, 190, 2.0)])
 def test_attention_in_blocks_with_capped_scores_and_a_unit_sink(dtype, heads, kv_heads, dim, chunk, cap):
     """Prompts, continuations across a block's edge and single tokens over more than one chunk of keys, each against the
     reference; scores are wide enough that the cap bends most of them."""
@@ -160,7 +160,7 @@ def test_attention_in_blocks_with_capped_scores_and_a_unit_sink(dtype, heads, kv
         close(out, want, dtype, f"spans {span}", f32=2e-5, bf16=2e-2)
 
 
-@pytest.mark.parametrize("heads,kv_heads,dim,chunk,cap", [(4, 1, 64, 128, 30.0), (8, 4, 96, 200, 30.0), (2, 2, 32, 70, 0.0), (6, 2, 128, 64, 4.0)])
+@pytest.mark.parametrize("heads,kv_heads,dim,chunk,cap", [(4, 1, 64, 128, 20.0), (6, 3, 96, 190, 12.0), (2, 2, 32, 70, 0.0), (6, 2, 128, 64, 4.0)])
 def test_tensor_core_attention_takes_the_block_mask_the_cap_and_the_sink(heads, kv_heads, dim, chunk, cap):
     """The bfloat16 kernels of prompts and of single tokens with the same options, against the reference: prompts,
     continuations across a block's edge, single tokens just inside and just outside a block, long and short together."""
@@ -391,26 +391,26 @@ def peaked(cfg, weights, seed):
 
 @pytest.mark.parametrize("dtype", BOTH)
 def test_keys_far_back_and_at_the_edges_of_blocks_and_pages(dtype, tmp_path):
-    """Blocks of 200 positions over pages of 64: a prompt that ends just inside and just outside a block, decoding across the
+    """Blocks of 150 positions over pages of 64: a prompt that ends just inside and just outside a block, decoding across the
     edge, with sharpened scores, against the plain implementation; then the same model with the masks' blocks made one
     position longer must differ at the edge (the test sees a block that is one token off)."""
     cfg = config(120, 48, 1e-6, 20.0, [
-        layer(attention(4, 2, 16, 16, 200, 8, 250000.0, 1.0, 30.0), 64),
-        layer(attention(4, 2, 16, 16, 200, 8, 250000.0, 1.0, 30.0, kv_from=0), None),
+        layer(attention(4, 2, 16, 16, 150, 8, 40000.0, 1.0, 25.0), 64),
+        layer(attention(4, 2, 16, 16, 150, 8, 40000.0, 1.0, 25.0, kv_from=0), None),
         layer(mlstm(2, 8, 12), 32)])
     weights = peaked(cfg, plain.random_weights(cfg, 11), 11)
     model, _, _ = build(cfg, tmp_path, dtype, weights=weights)
     cache = model.new_cache(64 * 16, 2)
     tokens = random_tokens(cfg["vocab"], 460, 5)
     want = plain.forward_logits(cfg, weights, tokens)
-    for cuts in ([460], [199], [200, 1, 1, 190, 9], [398]):
+    for cuts in ([460], [149], [150, 1, 1, 140, 9], [298]):
         logits_close(run(model, cache, tokens, cuts), want, dtype, f"cuts {cuts}")
     off = copy.deepcopy(cfg)
     for lay in off["layers"][:2]:
-        lay["mixer"]["mask"]["size"] = 201
+        lay["mixer"]["mask"]["size"] = 151
     other = plain.forward_logits(off, weights, tokens)
     d = (other - want).abs().max(-1).values
-    assert float(d[:200].max()) < 1e-9 and float(d[200]) > 1e-3      # position 200 is where the two masks part
+    assert float(d[:150].max()) < 1e-9 and float(d[150]) > 1e-3      # position 150 is where the two masks part
 
 
 @pytest.mark.parametrize("dtype", BOTH)
