@@ -124,7 +124,8 @@ class ZebovikConfig(ModelConfig):
         if kind == "attention":
             own = m.get("kv_from") is None
             dims = int(m["rot"]["dims"])
-            position = PartSpec("rotary_half", {"head_dim": int(m["dim"]), "rotary_dim": dims, "theta": float(m["rot"]["base"])}) \
+            position = PartSpec("rotary_half", {"head_dim": int(m["dim"]), "rotary_dim": dims, "theta": float(m["rot"]["base"]),
+                                                "precise": True}) \
                 if dims else None
             tensors = {"q_weight": p + "q", "q_bias": p + "q.b", "o_weight": p + "o"}
             if own:

@@ -59,7 +59,16 @@ ZEB_ONES = config(97, 40, 1e-6, 50.0, [
     layer(mlstm(1, 20, 28, 2.0), None),
 ])
 
-CONFIGS = {"odd": ZEB_ODD, "fast": ZEB_FAST, "ones": ZEB_ONES}
+# wide states: more rows than one pass of the scan's smallest form holds, a state-space layer of 144 rows under seven
+# taps, values wider than keys at a size the tensor-core kernels take (keys padded with zeros), blocks of one page
+ZEB_WIDE = config(150, 72, 1e-5, 25.0, [
+    layer(attention(2, 2, 96, 128, 64, 48, 20000.0, 0.2, 40.0), 80),
+    layer(mlstm(1, 160, 33, 5.0), None),
+    layer(mamba2(4, 16, 144, 2, 7, 4), 56),
+    layer(attention(2, 2, 96, 128, 100, 48, 20000.0, 0.1, 12.0, kv_from=0), None),
+])
+
+CONFIGS = {"odd": ZEB_ODD, "fast": ZEB_FAST, "ones": ZEB_ONES, "wide": ZEB_WIDE}
 
 
 def make_model_dir(cfg: dict, seed: int, folder=None, store_dtype=torch.float32, weights=None):
